@@ -30,17 +30,19 @@ class CacheManager:
     def __init__(self, needs: Sequence, cache_of: Sequence[Optional[int]], page_size: int, total_blocks,
                  num_slots: int, dtype: torch.dtype, device):
         """needs[i]: PagedKV | FixedState | None for order item i (None: no cache of
-        its own); cache_of[i]: the item whose cache item i reads, or None.
+        its own), or a tuple of these for an item that keeps several things; needs beyond the run order belong to
+        parts outside the layers (the embedding); cache_of[i]: the item whose cache item i reads, or None.
         total_blocks: pages of every paged group (an int) or one count per group."""
         self.page_size, self.num_slots, self.dtype, self.device = int(page_size), int(num_slots), dtype, torch.device(device)
         self.paged_keys: list[PagedKV] = []
         self.state_keys: list[FixedState] = []
-        self._item_group: list[Optional[tuple[str, int, int]]] = []   # (family, group, index in group)
+        # per item: (family, group, index in group), a list of these for an item with several needs, or None
+        self._item_group: list = []
         members: dict[tuple[str, int], int] = {}
-        for need in needs:
+
+        def place(need):
             if need is None:
-                self._item_group.append(None)
-                continue
+                return None
             if isinstance(need, PagedKV):
                 fam, keys = "paged", self.paged_keys
             elif isinstance(need, FixedState):
@@ -52,7 +54,10 @@ class CacheManager:
             g = keys.index(need)
             idx = members.get((fam, g), 0)
             members[(fam, g)] = idx + 1
-            self._item_group.append((fam, g, idx))
+            return (fam, g, idx)
+        for need in needs:
+            self._item_group.append([place(n) for n in need] if isinstance(need, (tuple, list)) else place(need))
+        cache_of = list(cache_of) + [None] * (len(needs) - len(cache_of))
         for i, src in enumerate(cache_of):
             if src is not None:
                 self._item_group[i] = self._item_group[src]
@@ -149,20 +154,23 @@ class CacheManager:
     def bindings(self, block_tables: Sequence[torch.Tensor]) -> list[CacheBinding]:
         """One CacheBinding per order item for a step whose block tables
         (one [B, blocks] int32 tensor per paged group) are given."""
-        out = []
-        for i, ig in enumerate(self._item_group):
+        def one(ig, writes: bool) -> CacheBinding:
             if ig is None:
-                out.append(CacheBinding())
-                continue
+                return CacheBinding()
             fam, g, idx = ig
             if fam == "paged":
-                out.append(CacheBinding(need=self.paged_keys[g], writes=not self._borrowed[i],
-                                        k=self.k_pools[g][idx], v=self.v_pools[g][idx] if self.v_pools[g] is not None else None,
-                                        block_table=block_tables[g], page_size=self.page_size,
-                                        num_pages=self.group_pages[g]))
+                return CacheBinding(need=self.paged_keys[g], writes=writes,
+                                    k=self.k_pools[g][idx], v=self.v_pools[g][idx] if self.v_pools[g] is not None else None,
+                                    block_table=block_tables[g], page_size=self.page_size, num_pages=self.group_pages[g])
+            return CacheBinding(need=self.state_keys[g], writes=writes, state=self.states[g][idx], num_slots=self.num_slots)
+        out = []
+        for i, ig in enumerate(self._item_group):
+            writes = not self._borrowed[i]
+            if isinstance(ig, list):
+                parts = tuple(one(x, writes) for x in ig)
+                out.append(CacheBinding(need=tuple(p.need for p in parts), writes=writes, parts=parts))
             else:
-                out.append(CacheBinding(need=self.state_keys[g], writes=not self._borrowed[i],
-                                        state=self.states[g][idx], num_slots=self.num_slots))
+                out.append(one(ig, writes))
         return out
 
     def bytes_per_token(self) -> int:

@@ -57,6 +57,7 @@ class ModelPlan:
     order: tuple[OrderEntry, ...]
     eos_token_id: Optional[int] = None
     bos_token_id: Optional[int] = None
+    unread_tensors: tuple = ()          # names a file may hold although no part reads them
 
     def __post_init__(self):
         sizes = {"vocab_size": self.vocab_size, "dim": self.hidden_size}

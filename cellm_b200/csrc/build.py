@@ -34,7 +34,8 @@ LIBRARIES: dict[str, tuple[str, list[str], list[str]]] = {
     "kernels_common": ("nvcc", ["kernels/embed.cu", "kernels/add_rmsnorm.cu", "kernels/short_conv.cu",
                                 "kernels/qk_norm_rope.cu", "kernels/swiglu.cu", "kernels/sample.cu",
                                 "kernels/attention_plain.cu", "kernels/gated_norm.cu", "kernels/mingru.cu",
-                                "kernels/latent.cu", "kernels/attn_prep.cu", "kernels/routed.cu"], []),
+                                "kernels/latent.cu", "kernels/attn_prep.cu", "kernels/routed.cu", "kernels/stream_ops.cu",
+                                "kernels/sink_attn_prep.cu", "kernels/recurrent.cu"], []),
     "gemm_plain": ("nvcc", ["kernels/gemm_plain.cu"], []),
     "gemm_tcgen05": ("nvcc", ["kernels/gemm_tcgen05.cu"], []),
     "attention_flash": ("nvcc", ["kernels/attention_flash.cu"], []),

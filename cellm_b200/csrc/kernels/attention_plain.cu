@@ -22,7 +22,8 @@ attention_plain_kernel(TA* __restrict__ out, const TA* __restrict__ q, const TA*
                        const TA* __restrict__ v_pool, const int* __restrict__ positions,
                        const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
                        int bt_stride, int num_pages, int page_size, int nh, int nkv, int hd, int hdv, int v_row, float scale,
-                       int window, int* __restrict__ err) {
+                       int window, const float* __restrict__ sinks, const float* __restrict__ unrot, int interleaved,
+                       int* __restrict__ err) {
     constexpr int CH = ATTN_PLAIN_THREADS;
     extern __shared__ float smem[];
     float* qs = smem;             // [hd]
@@ -94,7 +95,43 @@ attention_plain_kernel(TA* __restrict__ out, const TA* __restrict__ q, const TA*
             }
         }
     }
+    if (sinks) {
+        // a sink: one more term exp(sink_h) in the denominator, with no key and no value
+        const float sk = sinks[h];
+        const float m_new = fmaxf(m, sk);
+        const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
+        l = l * corr + expf(sk - m_new);
+#pragma unroll
+        for (int r = 0; r < ATTN_PLAIN_MAX_HD / CH; ++r) acc[r] *= corr;
+    }
     const float inv = 1.0f / l;
+    if (unrot) {
+        // values were cached rotated by their own positions: the sum is turned back by the token's position
+        // (pair m by -pos * f_m; f as [hdv/2][2] floats, high part and remainder)
+        float* ov = smem;                   // the queries are not needed any more
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < ATTN_PLAIN_MAX_HD / CH; ++r) {
+            const int d = threadIdx.x + r * CH;
+            if (d < hdv) ov[d] = acc[r] * inv;
+        }
+        __syncthreads();
+        const int half = hdv / 2;
+        for (int mm = threadIdx.x; mm < half; mm += CH) {
+            const float hi = unrot[2 * mm], lo = unrot[2 * mm + 1], fp = (float)pos;
+            const float a = fp * hi;
+            const float e = fmaf(fp, hi, -a) + fp * lo;
+            float sn, cs, se, ce;
+            sincosf(a, &sn, &cs);
+            sincosf(e, &se, &ce);
+            const float c = cs * ce - sn * se, s = sn * ce + cs * se;
+            const int i0 = interleaved ? 2 * mm : mm, i1 = interleaved ? 2 * mm + 1 : mm + half;
+            const float u = ov[i0], v = ov[i1];
+            out[(size_t)t * nh * hdv + (size_t)h * hdv + i0] = from_float<TA>(u * c + v * s);
+            out[(size_t)t * nh * hdv + (size_t)h * hdv + i1] = from_float<TA>(v * c - u * s);
+        }
+        return;
+    }
 #pragma unroll
     for (int r = 0; r < ATTN_PLAIN_MAX_HD / CH; ++r) {
         const int d = threadIdx.x + r * CH;
@@ -109,20 +146,23 @@ static int attention_plain_impl(void* out, const void* q, const void* k_pool, co
                                 const int* positions, const int* seq_of_token, const int* block_table,
                                 int bt_stride, int num_pages, int page_size, int T, int nh, int nkv,
                                 int hd, int hdv, int v_row, float scale, int window, int dtype, int* err,
-                                cudaStream_t stream) {
+                                cudaStream_t stream, const float* sinks = nullptr, const float* unrot = nullptr,
+                                int interleaved = 0) {
     if (T <= 0) return CELLM_OK;
+    if (unrot && hdv % 2) return CELLM_ERR_SIZE;
     if (hd > ATTN_PLAIN_MAX_HD || hd <= 0 || hdv <= 0 || hdv > v_row || hdv > ATTN_PLAIN_MAX_HD || nkv <= 0 || nh % nkv) return CELLM_ERR_SIZE;
-    const size_t smem = (size_t)(hd + 2 * ATTN_PLAIN_THREADS) * sizeof(float);
+    // the first hd floats hold the query; the output is turned back in the same place (hdv floats)
+    const size_t smem = (size_t)((hd > hdv ? hd : hdv) + 2 * ATTN_PLAIN_THREADS) * sizeof(float);
     const unsigned grid = (unsigned)T * (unsigned)nh;
     if (dtype == CELLM_F32)
         CELLM_RUN(attention_plain_kernel<float>, grid, ATTN_PLAIN_THREADS, smem, stream,
             (float*)out, (const float*)q, (const float*)k_pool, (const float*)v_pool, positions, seq_of_token,
-            block_table, bt_stride, num_pages, page_size, nh, nkv, hd, hdv, v_row, scale, window, err);
+            block_table, bt_stride, num_pages, page_size, nh, nkv, hd, hdv, v_row, scale, window, sinks, unrot, interleaved, err);
     else if (dtype == CELLM_BF16)
         CELLM_RUN(attention_plain_kernel<__nv_bfloat16>, grid, ATTN_PLAIN_THREADS, smem, stream,
             (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
             (const __nv_bfloat16*)v_pool, positions, seq_of_token, block_table, bt_stride, num_pages,
-            page_size, nh, nkv, hd, hdv, v_row, scale, window, err);
+            page_size, nh, nkv, hd, hdv, v_row, scale, window, sinks, unrot, interleaved, err);
     else return CELLM_ERR_DTYPE;
     return CELLM_OK;
 }
@@ -147,4 +187,16 @@ CELLM_API int cellm_attention_plain_wide(void* out, const void* q, const void* k
                                          cudaStream_t stream) {
     return attention_plain_impl(out, q, k_pool, v_pool, positions, seq_of_token, block_table, bt_stride, num_pages, page_size, T, nh, nkv,
                                 hd, hdv, hdv, scale, window, dtype, err, stream);
+}
+
+// The same with a learned sink per head in the softmax's denominator (`sinks` [nh], 32-bit; null: none) and with the
+// output turned back by the token's position (`unrot` [hdv/2][2]: the values' frequencies; null: values were
+// not rotated). Values have rows of their own width hdv.
+CELLM_API int cellm_attention_plain_sink(void* out, const void* q, const void* k_pool, const void* v_pool,
+                                         const int* positions, const int* seq_of_token, const int* block_table,
+                                         int bt_stride, int num_pages, int page_size, int T, int nh, int nkv,
+                                         int hd, int hdv, float scale, int window, const float* sinks, const float* unrot,
+                                         int interleaved, int dtype, int* err, cudaStream_t stream) {
+    return attention_plain_impl(out, q, k_pool, v_pool, positions, seq_of_token, block_table, bt_stride, num_pages, page_size, T, nh, nkv,
+                                hd, hdv, hdv, scale, window, dtype, err, stream, sinks, unrot, interleaved);
 }

@@ -62,6 +62,7 @@ class DecoderModel:
                 a, b = self.cache_need(i), self.cache_need(e.cache_of)
                 if a != b:
                     raise ConfigError(f"layer order item {i} needs {a} but item {e.cache_of} keeps {b}")
+        self.cache_needs()          # numbers the embedding's own cache item, if it keeps something per request
         self.program = None         # the model as records of the native executor, made at the first forward pass
 
     def cache_need(self, item: int):
@@ -70,8 +71,14 @@ class DecoderModel:
         return self.mixer_classes[self.plan.order[item].layer].cache_need(spec.params)
 
     def cache_needs(self) -> list:
-        """Per order item: its need, or None when it has no cache of its own."""
-        return [None if e.cache_of is not None else self.cache_need(i) for i, e in enumerate(self.plan.order)]
+        """Per order item: its need, or None when it has no cache of its own; then, if the embedding keeps
+        something per request, its need as one more item (`embedding.cache_item` is its index)."""
+        needs = [None if e.cache_of is not None else self.cache_need(i) for i, e in enumerate(self.plan.order)]
+        extra = type(self.embedding).cache_need(self.plan.embedding.params)
+        if extra is not None:
+            self.embedding.cache_item = len(needs)
+            needs.append(extra)
+        return needs
 
     def forward(self, ctx: StepContext, bindings: list[CacheBinding], logit_rows: Optional[torch.Tensor],
                 max_layers: Optional[int] = None) -> Optional[torch.Tensor]:

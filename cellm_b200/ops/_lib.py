@@ -47,6 +47,17 @@ _SIGNATURES = {
         "cellm_take_pending_tokens": [P, P, P, P, I, I, P, P],
         "cellm_keep_last_tokens": [P, P, P, I, I, P],
         "cellm_sample": [P, P, I, I, P, P, P, P, P, I, I, P, P],
+        "cellm_embed_pairs": [P, P, I, P, P, L, L, L, P, L, I, P, P, P, P, I, I, I, F, P, P],
+        "cellm_norm_pair": [P, P, P, P, P, I, I, I, F, I, P],
+        "cellm_scaled_add2": [P, P, P, F, L, I, P],
+        "cellm_pair_norm_mean": [P, P, P, P, P, I, I, F, I, P],
+        "cellm_conv_state_update": [P, L, I, P, P, P, L, I, P, I, I, I, P, P],
+        "cellm_sink_attn_prep": [P, P, P, P, L, I, P, P, I, P, L, I, P, P, F, P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P],
+        "cellm_attention_plain_sink": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P, I, I, P, P],
+        "cellm_hgrn2_scan": [P, P, L, I, P, L, I, I, I, P, P, P, P, I, I, I, I, P, P],
+        "cellm_delta_prep": [P, P, P, P, P, L, I, I, P, I, P, L, I, P, P, P, P, P, P, I, I, I, I, I, F, P, P],
+        "cellm_delta_scan": [P, P, L, I, P, P, P, P, P, P, I, I, I, I, I, P, P],
+        "cellm_head_norm_gate": [P, P, P, P, L, I, I, I, F, I, P],
     },
     "gemm_plain": {
         "cellm_gemm_plain": [P, P, P, I, I, I, L, L, L, I, I, P],

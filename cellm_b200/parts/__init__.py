@@ -3,5 +3,5 @@ from .base import (Block, CacheBinding, Embedding, FeedForward, FixedState, Head
                    Residual, StepContext, TensorSpec)
 from .registry import (part_class, register_block, register_embedding, register_feed_forward, register_head,
                        register_mixer, register_norm, register_position, registered)
-from . import (attention, block, embedding, gated_mlp, latent_attention, mingru, norm, rope, routed_experts, short_conv,  # noqa: F401
-               swiglu)
+from . import (attention, block, dense_mlp, embedding, gated_mlp, latent_attention, linear_recurrence, mingru, norm, rope,  # noqa: F401
+               routed_experts, short_conv, sink_attention, swiglu)

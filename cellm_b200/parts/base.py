@@ -103,6 +103,8 @@ class CacheBinding:
     # fixed state
     state: Optional[torch.Tensor] = None      # [slots, *shape]
     num_slots: int = 0
+    # an item that declared several needs (a tuple): one binding per need, in the order declared
+    parts: tuple = ()
 
 
 class Residual:
@@ -143,6 +145,12 @@ class Part:
 
 
 class Embedding(Part):
+    @classmethod
+    def cache_need(cls, params: dict):
+        """What the embedding keeps per request (a FixedState, say for the request's last token), or None. An
+        embedding with a need is called as forward(token_ids, ctx, cache)."""
+        return None
+
     def forward(self, token_ids: torch.Tensor, ctx: "StepContext") -> torch.Tensor:
         """The start of the residual stream: float32 [T, hidden]."""
         raise NotImplementedError
@@ -190,7 +198,9 @@ class Mixer(Part):
 
     @classmethod
     def cache_need(cls, params: dict):
-        """PagedKV, FixedState or None."""
+        """PagedKV, FixedState, None, or a tuple of these when the mixer keeps several things (pages of keys and
+        values beside a convolution's last inputs and a recurrent state, say); its binding then has one binding per
+        need in `parts`."""
         return None
 
     can_read_foreign_cache = False   # whether an order item may set cache_of for this mixer

@@ -54,6 +54,42 @@ class ParallelBlock(Block):
 register_block("parallel", ParallelBlock)
 
 
+class TwoNormParallelBlock(Block):
+    """A layer whose mixer and feed-forward read the same stream through a norm each, and whose sum joins the stream
+    times a constant:  x += mult * (mixer(norm1(x)) + feed_forward(norm2(x))). The layer may have no feed-forward.
+    Both norms must be RMS norms with one eps and no groups: the stream is read once for both. The sum is 32-bit.
+
+    params: residual_mult (default 1)."""
+    graph_safe = True
+
+    def __init__(self, mixer_norm, mixer, feed_forward_norm, feed_forward, params=None, weights=None, dtype=None):
+        from ..config.errors import ConfigError
+        self.mixer_norm, self.mixer = mixer_norm, mixer
+        self.feed_forward_norm, self.feed_forward = feed_forward_norm, feed_forward
+        self.mult = float((params or {}).get("residual_mult", 1.0))
+        self.dtype = dtype
+        if (feed_forward is None) != (feed_forward_norm is None):
+            raise ConfigError("parallel_two_norms: a feed-forward and its norm come together")
+        for n in (mixer_norm, feed_forward_norm):
+            if n is not None and (not all(hasattr(n, a) for a in ("weight", "eps", "groups")) or n.groups != 1):
+                raise ConfigError("parallel_two_norms: the norms must be RMS norms without groups")
+        if feed_forward_norm is not None and (feed_forward_norm.eps != mixer_norm.eps or
+                                              feed_forward_norm.weight.dtype != mixer_norm.weight.dtype):
+            raise ConfigError("parallel_two_norms: the two norms must have one eps and one element type")
+
+    def forward(self, residual: Residual, ctx: StepContext, cache: CacheBinding) -> None:
+        from .. import ops
+        x = residual.flush()
+        n1, n2 = self.mixer_norm, self.feed_forward_norm
+        y1, y2 = ops.norm_pair(x, n1.weight, n2.weight if n2 is not None else None, n1.eps, self.dtype)
+        a = self.mixer.forward(y1, ctx, cache)
+        b = self.feed_forward.forward(y2, ctx) if self.feed_forward is not None else None
+        ops.scaled_add2(x, a, b, self.mult)
+
+
+register_block("parallel_two_norms", TwoNormParallelBlock)
+
+
 class GatedPostNormBlock(Block):
     """A layer whose sublayers read the residual stream itself and whose norm sits on the sublayer's result:
 

@@ -1,0 +1,38 @@
+"""Plain two-matrix feed-forward: W_down act(W_up h), with act one of "relu2" (the square of relu), "relu", "silu",
+"gelu", "gelu_tanh". The first product keeps its 32-bit sums until the activation is formed."""
+from __future__ import annotations
+
+import torch
+
+from ..config.errors import ConfigError
+from .base import FeedForward, StepContext, TensorSpec
+from .linear import Linear
+from .registry import register_feed_forward
+
+ACTIVATIONS = ("relu2", "relu", "silu", "gelu", "gelu_tanh")
+
+
+class DenseMLP(FeedForward):
+    graph_safe = True
+
+    """params: hidden_size, ff_dim, activation. weights: up [ff, H], down [H, ff]."""
+
+    @classmethod
+    def weight_specs(cls, params):
+        H, ff = params["hidden_size"], params["ff_dim"]
+        return {"up": TensorSpec((ff, H), "linear"), "down": TensorSpec((H, ff), "linear")}
+
+    def __init__(self, params: dict, weights: dict, dtype: torch.dtype):
+        self.H, self.ff, self.dtype = int(params["hidden_size"]), int(params["ff_dim"]), dtype
+        self.activation = params.get("activation", "relu2")
+        if self.activation not in ACTIVATIONS:
+            raise ConfigError(f"dense_mlp: activation {self.activation!r}; known: {list(ACTIVATIONS)}")
+        self.up, self.down = Linear(weights["up"], dtype), Linear(weights["down"], dtype)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        from .. import ops
+        u = self.up(x, out_dtype=torch.float32)
+        return self.down(ops.activation(u, self.activation, self.dtype))
+
+
+register_feed_forward("dense_mlp", DenseMLP)

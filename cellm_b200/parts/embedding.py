@@ -42,6 +42,38 @@ class TokenEmbedding(Embedding):
         return ops.embed(self.weight, token_ids, ctx.err, self.scale, self.positions, ctx.positions if self.positions is not None else None)
 
 
+class PairHashEmbedding(Embedding):
+    """The token's row times `scale`, plus a row of a second table chosen by a hash of the token and the one before it:
+    row (previous * mul_prev + token * mul_cur) mod buckets, and the table's last row (number `buckets`) for a
+    sequence's first token. The previous token of a portion's first token is the request's state (one int32 in its
+    slot), so a sequence cut anywhere finds the same rows.
+
+    params: vocab_size, dim, scale (default 1), buckets, mul_prev, mul_cur. weights: weight [vocab, dim],
+    pairs [buckets + 1, dim]."""
+    graph_safe = True
+
+    @classmethod
+    def weight_specs(cls, params):
+        return {"weight": TensorSpec((params["vocab_size"], params["dim"]), "embedding"),
+                "pairs": TensorSpec((params["buckets"] + 1, params["dim"]), "embedding")}
+
+    @classmethod
+    def cache_need(cls, params):
+        from .base import FixedState
+        return FixedState((1,), torch.int32)
+
+    def __init__(self, params: dict, weights: dict, dtype: torch.dtype):
+        self.weight = weights["weight"].contiguous()
+        self.pairs = weights["pairs"].to(self.weight.dtype).contiguous()
+        self.scale = float(params.get("scale", 1.0))
+        self.buckets, self.mul_prev, self.mul_cur = int(params["buckets"]), int(params["mul_prev"]), int(params["mul_cur"])
+
+    def forward(self, token_ids: torch.Tensor, ctx, cache=None) -> torch.Tensor:
+        if cache is None or cache.state is None:
+            raise ValueError("lookup_pairs: the embedding needs its state (every request's last token)")
+        return ops.embed_pairs(self.weight, self.pairs, self.buckets, self.mul_prev, self.mul_cur, self.scale, cache.state, ctx)
+
+
 class LinearHead(Head):
     graph_safe = True
 
@@ -66,4 +98,5 @@ class LinearHead(Head):
 
 
 register_embedding("lookup", TokenEmbedding)
+register_embedding("lookup_pairs", PairHashEmbedding)
 register_head("linear", LinearHead)

@@ -1,0 +1,205 @@
+"""Mixers whose state is a matrix per head, S [dim, value_dim] in 32-bit floats in the request's slot (zero at its start).
+
+`hgrn2`: linear attention in which the forget gate also decides what is written.
+
+    q = silu(W_q h)    v = W_v h    f = l + (1 - l) sigmoid(W_f h + b_f)      (l: a learned lower bound per channel)
+    S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T        o_t = S_t^T q_t
+    out = W_o (rms_norm(o_t per head) * w, heads side by side)
+
+`gated_delta`: the gated delta rule with one decay per head and key channel.
+
+    q, k, v = silu(conv(W h))   (a short causal convolution over time per channel)
+    q, k unit vectors per head (x / sqrt(sum x^2 + 1e-6)), q also times dim^-1/2;   beta = sigmoid(W_b h)
+    g = exp(-exp(A_log_h) * softplus(W_a2 (W_a1 h) + dt_bias))     per head and key channel
+    S <- diag(g) S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
+    out = W_o (rms_norm(o per head) * w * sigmoid(W_g2 (W_g1 h)))
+    Value head h reads the q and k of head floor(h / (heads / qk_heads)).
+
+Everything that enters a recurrence is 32-bit (the projections keep their 32-bit sums; gates, decays, unit vectors and
+the state are computed in 32-bit), and a request's tokens are walked in order from the state the step before left, so
+the state after a token does not depend on how the sequence was cut. The delta rule also keeps the convolution's last
+taps - 1 projected rows in the slot."""
+from __future__ import annotations
+
+import torch
+
+from ..config.errors import ConfigError
+from .base import CacheBinding, FixedState, Mixer, StepContext, TensorSpec
+from .linear import Linear, stack_rows
+from .registry import register_mixer
+from .sink_attention import bindings_of
+
+
+def _f32(weights: dict, *names) -> torch.Tensor:
+    return torch.cat([weights[n].to(torch.float32).reshape(-1) for n in names]).contiguous()
+
+
+class Hgrn2Mixer(Mixer):
+    graph_safe = True
+
+    """params: hidden_size, heads, dim, value_dim, eps, out_dtype32 (default False).
+    weights: q, f [heads*dim, H]; f_bias, lower [heads*dim]; v [heads*vd, H]; norm [vd]; o [H, heads*vd]."""
+
+    @classmethod
+    def weight_specs(cls, params):
+        H, h, d, vd = (int(params[k]) for k in ("hidden_size", "heads", "dim", "value_dim"))
+        return {"q": TensorSpec((h * d, H), "linear"), "f": TensorSpec((h * d, H), "linear"), "f_bias": TensorSpec((h * d,), "bias"),
+                "lower": TensorSpec((h * d,), "unit_interval"), "v": TensorSpec((h * vd, H), "linear"),
+                "norm": TensorSpec((vd,), "norm"), "o": TensorSpec((H, h * vd), "linear")}
+
+    @classmethod
+    def cache_need(cls, params):
+        return FixedState((int(params["heads"]), int(params["dim"]), int(params["value_dim"])), torch.float32)
+
+    def __init__(self, params: dict, weights: dict, dtype: torch.dtype):
+        self.H, self.heads, self.dim, self.vd = (int(params[k]) for k in ("hidden_size", "heads", "dim", "value_dim"))
+        self.eps, self.dtype = float(params["eps"]), dtype
+        self.in_proj = Linear(stack_rows(weights["q"], weights["f"], weights["v"]), dtype)
+        self.out_proj = Linear(weights["o"], dtype)
+        self.out32 = bool(params.get("out_dtype32", False))
+        self.f_bias, self.lower, self.norm_w = _f32(weights, "f_bias"), _f32(weights, "lower"), _f32(weights, "norm")
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
+        from .. import ops
+        state = bindings_of(cache, 1)[0].state
+        hd = self.heads * self.dim
+        proj = self.in_proj(x, out_dtype=torch.float32)
+        o = ops.hgrn2_scan(proj, 0, hd, 2 * hd, self.f_bias, self.lower, state, ctx, self.heads, self.dim, self.vd)
+        y = ops.head_norm_gate(o, self.norm_w, None, self.heads, self.vd, self.eps, self.dtype)
+        return self.out_proj(y, out_dtype=torch.float32 if self.out32 else None)
+
+
+register_mixer("hgrn2", Hgrn2Mixer)
+
+
+class GatedDeltaMixer(Mixer):
+    graph_safe = True
+
+    """params: hidden_size, heads, qk_heads, dim, value_dim, conv_taps, eps, decay_rank, gate_rank (-1: whatever the
+    file's tensors have), unit_eps (default 1e-6).
+    weights: q, k [qk_heads*dim, H]; v [heads*vd, H]; q_conv, k_conv [qk_heads*dim, taps]; v_conv [heads*vd, taps];
+    beta [heads, H]; a1 [decay_rank, H], a2 [heads*dim, decay_rank], dt_bias [heads*dim], A_log [heads];
+    g1 [gate_rank, H], g2 [heads*vd, gate_rank]; norm [vd]; o [H, heads*vd]."""
+
+    @classmethod
+    def weight_specs(cls, params):
+        H, h, g, d, vd, taps = (int(params[k]) for k in ("hidden_size", "heads", "qk_heads", "dim", "value_dim", "conv_taps"))
+        ra, rg = int(params.get("decay_rank", -1)), int(params.get("gate_rank", -1))
+        return {"q": TensorSpec((g * d, H), "linear"), "k": TensorSpec((g * d, H), "linear"), "v": TensorSpec((h * vd, H), "linear"),
+                "q_conv": TensorSpec((g * d, taps), "conv_tap_wide"), "k_conv": TensorSpec((g * d, taps), "conv_tap_wide"),
+                "v_conv": TensorSpec((h * vd, taps), "conv_tap_wide"), "beta": TensorSpec((h, H), "linear"),
+                "a1": TensorSpec((ra, H), "linear"), "a2": TensorSpec((h * d, ra), "linear_wide"), "dt_bias": TensorSpec((h * d,), "bias"),
+                "A_log": TensorSpec((h,), "log_rate"), "g1": TensorSpec((rg, H), "linear"), "g2": TensorSpec((h * vd, rg), "linear_wide"),
+                "norm": TensorSpec((vd,), "norm"), "o": TensorSpec((H, h * vd), "linear")}
+
+    @classmethod
+    def cache_need(cls, params):
+        h, g, d, vd, taps = (int(params[k]) for k in ("heads", "qk_heads", "dim", "value_dim", "conv_taps"))
+        state = FixedState((h, d, vd), torch.float32)
+        if taps > 1:
+            return (FixedState((taps - 1, 2 * g * d + h * vd), torch.float32), state)
+        return state
+
+    def __init__(self, params: dict, weights: dict, dtype: torch.dtype):
+        self.H, self.heads, self.qkh, self.dim, self.vd, self.taps = (
+            int(params[k]) for k in ("hidden_size", "heads", "qk_heads", "dim", "value_dim", "conv_taps"))
+        if self.heads % self.qkh:
+            raise ConfigError(f"gated_delta: {self.heads} heads are not a multiple of {self.qkh} query/key heads")
+        self.eps, self.unit_eps, self.dtype = float(params["eps"]), float(params.get("unit_eps", 1e-6)), dtype
+        self.ra, self.rg = int(weights["a1"].shape[0]), int(weights["g1"].shape[0])
+        if weights["a2"].shape[1] != self.ra or weights["g2"].shape[1] != self.rg:
+            raise ConfigError("gated_delta: the two matrices of a low-rank product do not fit each other")
+        self.in_proj = Linear(stack_rows(weights["q"], weights["k"], weights["v"], weights["beta"]), dtype)
+        self.low_proj = Linear(stack_rows(weights["a1"], weights["g1"]), dtype)
+        self.a2, self.g2 = Linear(weights["a2"], dtype), Linear(weights["g2"], dtype)
+        self.out_proj = Linear(weights["o"], dtype)
+        self.conv_w = torch.cat([weights[n].to(torch.float32) for n in ("q_conv", "k_conv", "v_conv")], dim=0).contiguous()
+        self.dt_bias, self.A_log, self.norm_w = _f32(weights, "dt_bias"), _f32(weights, "A_log"), _f32(weights, "norm")
+        self.n_needs = 2 if self.taps > 1 else 1
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
+        from .. import ops
+        b = bindings_of(cache, self.n_needs)
+        conv_state = b[0].state if self.taps > 1 else None
+        state = b[-1].state
+        proj = self.in_proj(x, out_dtype=torch.float32)
+        low = self.low_proj(x)
+        a = self.a2(low[:, :self.ra], out_dtype=torch.float32)
+        gate = self.g2(low[:, self.ra:], out_dtype=torch.float32)
+        C = 2 * self.qkh * self.dim + self.heads * self.vd
+        qk, v, beta, decay = ops.delta_prep(proj, 0, C, self.conv_w, self.taps, conv_state, a, self.dt_bias, self.A_log, ctx,
+                                            self.heads, self.qkh, self.dim, self.vd, self.unit_eps)
+        if conv_state is not None:
+            ops.conv_state_update(conv_state, proj, 0, None, self.taps, ctx)
+        o = ops.delta_scan(qk, v, beta, decay, state, ctx, self.heads, self.qkh, self.dim, self.vd)
+        y = ops.head_norm_gate(o, self.norm_w, gate, self.heads, self.vd, self.eps, self.dtype)
+        return self.out_proj(y)
+
+
+register_mixer("gated_delta", GatedDeltaMixer)
+
+
+class SideBySideMixer(Mixer):
+    graph_safe = True
+
+    """Two mixers that read the same input; the result is half the sum of their outputs, each first RMS-normed over the
+    model's width with a plain weight of its own:  out = (rms_norm(A(h)) * w_a + rms_norm(B(h)) * w_b) / 2.
+    Both keep their own caches: the item's needs are the first mixer's followed by the second's.
+
+    params: hidden_size, eps, first, second (PartSpecs of registered mixers; their weights' names are prefixed
+    `first.` and `second.` here). weights: first_out, second_out [H] and the two mixers' own."""
+
+    @staticmethod
+    def _subs(params):
+        from .registry import part_class
+        return [(name, params[name], part_class("mixer", params[name].kind)) for name in ("first", "second")]
+
+    @classmethod
+    def weight_specs(cls, params):
+        H = int(params["hidden_size"])
+        specs = {"first_out": TensorSpec((H,), "norm"), "second_out": TensorSpec((H,), "norm")}
+        for name, spec, klass in cls._subs(params):
+            for local, ts in klass.weight_specs(spec.params).items():
+                specs[f"{name}.{local}"] = ts
+        return specs
+
+    @classmethod
+    def cache_need(cls, params):
+        needs = []
+        for name, spec, klass in cls._subs(params):
+            n = klass.cache_need(spec.params)
+            needs += list(n) if isinstance(n, (tuple, list)) else ([n] if n is not None else [])
+        return tuple(needs) if len(needs) != 1 else needs[0]
+
+    def __init__(self, params: dict, weights: dict, dtype: torch.dtype):
+        self.H, self.eps, self.dtype = int(params["hidden_size"]), float(params["eps"]), dtype
+        self.parts, self.counts = [], []
+        for name, spec, klass in self._subs(params):
+            own = {k[len(name) + 1:]: v for k, v in weights.items() if k.startswith(name + ".")}
+            sub_params = dict(spec.params)
+            sub_params.setdefault("out_dtype32", True)      # the norm over the result reads the product's 32-bit sums
+            self.parts.append(klass(sub_params, own, dtype))
+            n = klass.cache_need(spec.params)
+            self.counts.append(len(n) if isinstance(n, (tuple, list)) else (0 if n is None else 1))
+        self.first, self.second = self.parts
+        self.w_first, self.w_second = _f32(weights, "first_out"), _f32(weights, "second_out")
+
+    def _binding(self, cache: CacheBinding, start: int, n: int) -> CacheBinding:
+        every = cache.parts if cache.parts else (cache,)
+        mine = every[start:start + n]
+        if n == 1:
+            return mine[0]
+        return CacheBinding(need=tuple(p.need for p in mine), writes=cache.writes, parts=tuple(mine))
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
+        from .. import ops
+        a = self.first.forward(x, ctx, self._binding(cache, 0, self.counts[0]))
+        b = self.second.forward(x, ctx, self._binding(cache, self.counts[0], self.counts[1]))
+        if a.dtype != torch.float32:
+            a = a.to(torch.float32)
+        if b.dtype != torch.float32:
+            b = b.to(torch.float32)
+        return ops.pair_norm_mean(a.contiguous(), b.contiguous(), self.w_first, self.w_second, self.eps, self.dtype)
+
+
+register_mixer("side_by_side", SideBySideMixer)

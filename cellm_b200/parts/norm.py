@@ -2,7 +2,8 @@
 fused with the addition of whatever waits to be added to the residual stream. With `groups` > 1 the
 vector is split into that many equal consecutive parts and each is divided by its own root mean square.
 With `offset` c the stored weight lies around zero and the factor is c + w (formed once, in 32-bit, when the
-part is built: c + w has more digits than the stored type keeps)."""
+part is built: c + w has more digits than the stored type keeps).
+With `scalar` the stored weight is a single number that multiplies every coordinate."""
 from __future__ import annotations
 
 from typing import Optional
@@ -18,11 +19,12 @@ from .registry import register_norm
 class RMSNorm(Norm):
     graph_safe = True
 
-    """params: dim, eps, groups (default 1), offset (default 0). weights: weight [dim]."""
+    """params: dim, eps, groups (default 1), offset (default 0), scalar (default False). weights: weight [dim] ([] if scalar)."""
 
     @classmethod
     def weight_specs(cls, params):
-        return {"weight": TensorSpec((params["dim"],), "norm_offset" if params.get("offset") else "norm")}
+        shape = () if params.get("scalar") else (params["dim"],)
+        return {"weight": TensorSpec(shape, "norm_offset" if params.get("offset") else "norm")}
 
     def __init__(self, params: dict, weights: dict, dtype: torch.dtype):
         self.dim = int(params["dim"])
@@ -32,6 +34,8 @@ class RMSNorm(Norm):
             raise ConfigError(f"rms_norm: {self.dim} values do not split into {self.groups} equal groups")
         self.offset = float(params.get("offset", 0.0))
         self.weight = weights["weight"].contiguous()
+        if params.get("scalar"):        # one number for all coordinates: kept as a row of it, which the kernels read
+            self.weight = self.weight.reshape(1).expand(self.dim).contiguous()
         if self.offset:
             self.weight = (self.weight.to(torch.float32) + self.offset).contiguous()
         self.dtype = dtype

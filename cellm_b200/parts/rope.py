@@ -1,6 +1,10 @@
 """Rotary position encoding (crates/cellm-kernels/src/cpu_kernels.rs:264-292):
 pairs (i, i + rot/2) ("half") or (2i, 2i+1) ("interleaved") of the first
-`rotary_dim` values of a head turn by pos * theta^(-2i/rotary_dim)."""
+`rotary_dim` values of a head turn by pos * theta^(-2i/rotary_dim).
+
+With `scaling` {factor, low, high, original} the frequencies are stretched by wavelength: a frequency f whose
+wavelength l = 2 pi / f is shorter than original / high stays; one longer than original / low becomes f / factor;
+between the two, with s = (original / l - low) / (high - low), it becomes (1 - s) f / factor + s f."""
 from __future__ import annotations
 
 import torch
@@ -10,12 +14,26 @@ from .base import Position
 from .registry import register_position
 
 
-def split_inv_freq(theta: float, rotary_dim: int) -> torch.Tensor:
-    """theta^(-2i/rotary_dim) for i < rotary_dim/2, computed in 64-bit and given as
-    [rotary_dim/2, 2] float32: the nearest float and the remainder, so that the
+def scale_by_wavelength(inv: torch.Tensor, scaling: dict) -> torch.Tensor:
+    """64-bit frequencies stretched by wavelength (see the module's text)."""
+    import math
+    factor, low, high, original = (float(scaling[k]) for k in ("factor", "low", "high", "original"))
+    if factor <= 0 or high <= low or original <= 0:
+        raise ConfigError(f"rope: scaling {scaling!r} needs factor > 0, high > low and original > 0")
+    wavelength = 2.0 * math.pi / inv
+    s = ((original / wavelength - low) / (high - low)).clamp(0.0, 1.0)
+    mixed = (1.0 - s) * inv / factor + s * inv
+    return torch.where(wavelength < original / high, inv, torch.where(wavelength > original / low, inv / factor, mixed))
+
+
+def split_inv_freq(theta: float, rotary_dim: int, scaling: dict | None = None) -> torch.Tensor:
+    """theta^(-2i/rotary_dim) for i < rotary_dim/2 (stretched by `scaling` if given), computed in 64-bit and given
+    as [rotary_dim/2, 2] float32: the nearest float and the remainder, so that the
     kernel can form pos * inv_freq without losing the low bits."""
     i = torch.arange(rotary_dim // 2, dtype=torch.float64)
     inv = float(theta) ** (-(2.0 * i) / max(rotary_dim, 1))
+    if scaling:
+        inv = scale_by_wavelength(inv, scaling)
     hi = inv.to(torch.float32)
     lo = (inv - hi.to(torch.float64)).to(torch.float32)
     return torch.stack([hi, lo], dim=1).contiguous()
@@ -24,7 +42,7 @@ def split_inv_freq(theta: float, rotary_dim: int) -> torch.Tensor:
 class RotaryEmbedding(Position):
     graph_safe = True
 
-    """params: head_dim, rotary_dim, theta, layout ("half" | "interleaved")."""
+    """params: head_dim, rotary_dim, theta, layout ("half" | "interleaved"), scaling (None, or {factor, low, high, original})."""
 
     def __init__(self, params: dict, device):
         self.head_dim = int(params["head_dim"])
@@ -35,7 +53,8 @@ class RotaryEmbedding(Position):
             raise ConfigError(f"rope: layout {self.layout!r} is neither 'half' nor 'interleaved'")
         if self.rotary_dim % 2 or not 0 <= self.rotary_dim <= self.head_dim:
             raise ConfigError(f"rope: rotary_dim {self.rotary_dim} must be even and at most head_dim {self.head_dim}")
-        self.inv_freq = split_inv_freq(self.theta, self.rotary_dim).to(device)
+        self.scaling = params.get("scaling")
+        self.inv_freq = split_inv_freq(self.theta, self.rotary_dim, self.scaling).to(device)
 
     def rotation(self):
         return self.rotary_dim, self.layout == "interleaved", self.inv_freq

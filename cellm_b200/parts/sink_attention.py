@@ -1,0 +1,136 @@
+"""Windowed attention with a learned sink per head, short convolutions on its projections and rotated values.
+
+    q, k, v = W h (+ b);   each channel then passes a short causal convolution over time (optional)
+    q, k normed over the whole projection (all heads of a token by one root mean square, plain weights; optional)
+    q, k: the first `rotary_dim` entries of every head turn by pos * f_i (the position part: a rotation, frequencies
+          possibly stretched by wavelength)
+    v:    every value head turns over all its entries by its own position j, pair m by j * theta^(-2m/vd), and is
+          cached so; a head's output at position i (the weighted sum of values) is turned back by -i * theta^(-2m/vd)
+    softmax over the keys j with 0 <= i - j < window (window 0: all earlier keys); the denominator also holds
+          exp(sink_h): a learned number per head with no key and no value, not scaled, counted once
+    out = W_o (heads side by side)
+
+Scores, softmax, norms, angles and the convolutions' sums are 32-bit. The request keeps pages of keys and values
+(values with rows of their own width) and, beside them, the last taps - 1 projected rows (bias included) of q, k and v
+in its state slot, so a sequence cut anywhere sees the same convolution inputs.
+
+Kernels: one product for q | k | v with 32-bit sums, `sink_attn_prep` (bias, convolution, norm, rotations, cache
+write), `conv_state_update`, the attention itself (32-bit: the plain kernel with sink and turn-back; bfloat16: the
+same kernel), the output product."""
+from __future__ import annotations
+
+import torch
+
+from ..config.errors import ConfigError
+from ..config.plan import PartSpec
+from .base import CacheBinding, FixedState, Mixer, PagedKV, StepContext, TensorSpec
+from .linear import Linear, stack_rows
+from .registry import part_class, register_mixer
+from .rope import split_inv_freq
+
+
+def bindings_of(cache: CacheBinding, n: int) -> tuple:
+    """The n bindings of a mixer that declared n needs (one need: the binding itself)."""
+    if n == 1:
+        return (cache.parts[0] if cache.parts else cache,)
+    if len(cache.parts) != n:
+        raise ValueError(f"a mixer with {n} cache needs was given {len(cache.parts)} bindings")
+    return cache.parts
+
+
+class SinkAttentionMixer(Mixer):
+    graph_safe = True
+
+    """params: hidden_size, num_heads, num_kv_heads, head_dim, value_dim (default head_dim), scale, window (default 0),
+    bias (default False: q, k, v have none), conv_taps (default 0: no convolution), qk_norm_eps (None: no norm over the
+    projection), position (PartSpec of a rotation, or None), value_theta (None: values are not rotated),
+    sinks (default True), out_dtype32 (default False: out_proj's result in the activations' type).
+    weights: q_proj [nh*hd, H], k_proj [nkv*hd, H], v_proj [nkv*vd, H], out_proj [H, nh*vd]; q_bias, k_bias, v_bias;
+    q_conv [nh*hd, taps], k_conv, v_conv; q_norm [nh*hd], k_norm [nkv*hd]; sinks [nh]."""
+
+    @classmethod
+    def _sizes(cls, params):
+        nh, nkv, hd = int(params["num_heads"]), int(params["num_kv_heads"]), int(params["head_dim"])
+        return nh, nkv, hd, int(params.get("value_dim") or hd)
+
+    @classmethod
+    def weight_specs(cls, params):
+        H = params["hidden_size"]
+        nh, nkv, hd, vd = cls._sizes(params)
+        taps = int(params.get("conv_taps") or 0)
+        specs = {"q_proj": TensorSpec((nh * hd, H), "linear"), "k_proj": TensorSpec((nkv * hd, H), "linear"),
+                 "v_proj": TensorSpec((nkv * vd, H), "linear"), "out_proj": TensorSpec((H, nh * vd), "linear")}
+        if params.get("bias"):
+            specs.update(q_bias=TensorSpec((nh * hd,), "bias"), k_bias=TensorSpec((nkv * hd,), "bias"), v_bias=TensorSpec((nkv * vd,), "bias"))
+        if taps:
+            specs.update(q_conv=TensorSpec((nh * hd, taps), "conv_tap_wide"), k_conv=TensorSpec((nkv * hd, taps), "conv_tap_wide"),
+                         v_conv=TensorSpec((nkv * vd, taps), "conv_tap_wide"))
+        if params.get("qk_norm_eps") is not None:
+            specs.update(q_norm=TensorSpec((nh * hd,), "norm"), k_norm=TensorSpec((nkv * hd,), "norm"))
+        if params.get("sinks", True):
+            specs["sinks"] = TensorSpec((nh,), "sink")
+        return specs
+
+    @classmethod
+    def cache_need(cls, params):
+        nh, nkv, hd, vd = cls._sizes(params)
+        paged = PagedKV(nkv, hd, int(params.get("window") or 0), value_dim=vd if vd != hd else 0)
+        taps = int(params.get("conv_taps") or 0)
+        if taps > 1:
+            return (paged, FixedState((taps - 1, nh * hd + nkv * hd + nkv * vd), torch.float32))
+        return paged
+
+    def __init__(self, params: dict, weights: dict, dtype: torch.dtype):
+        self.H = int(params["hidden_size"])
+        self.nh, self.nkv, self.hd, self.vd = self._sizes(params)
+        if self.nh % self.nkv:
+            raise ConfigError(f"sink_attention: {self.nh} heads are not a multiple of {self.nkv} key/value heads")
+        self.scale, self.window = float(params["scale"]), int(params.get("window") or 0)
+        self.taps = int(params.get("conv_taps") or 0)
+        self.dtype = dtype
+        f32 = lambda *names: torch.cat([weights[n].to(torch.float32).reshape(-1) for n in names]).contiguous()
+        self.qkv = Linear(stack_rows(weights["q_proj"], weights["k_proj"], weights["v_proj"]), dtype)
+        self.out_proj = Linear(weights["out_proj"], dtype)
+        self.out32 = bool(params.get("out_dtype32", False))
+        self.bias = f32("q_bias", "k_bias", "v_bias") if params.get("bias") else None
+        self.conv_w = None
+        if self.taps:
+            self.conv_w = torch.cat([weights[n].to(torch.float32) for n in ("q_conv", "k_conv", "v_conv")], dim=0).contiguous()
+        self.eps = params.get("qk_norm_eps")
+        self.q_norm_w = self.k_norm_w = None
+        if self.eps is not None:
+            self.q_norm_w, self.k_norm_w = f32("q_norm"), f32("k_norm")
+        self.sinks = f32("sinks") if params.get("sinks", True) else None
+        dev = weights["q_proj"].device
+        pos: PartSpec | None = params.get("position")
+        self.position = part_class("position", pos.kind)(pos.params, dev) if pos is not None else None
+        self.rot, self.interleaved, self.qk_freq = 0, False, None
+        if self.position is not None:
+            r = self.position.rotation()
+            if r is None:
+                raise ConfigError("sink_attention: the position encoding must be a rotation")
+            self.rot, self.interleaved, self.qk_freq = int(r[0]), bool(r[1]), r[2]
+        self.v_freq = None
+        if params.get("value_theta") is not None:
+            if self.vd % 2:
+                raise ConfigError(f"sink_attention: values of {self.vd} entries cannot be rotated in pairs")
+            self.v_freq = split_inv_freq(float(params["value_theta"]), self.vd).to(dev)
+        self.n_needs = 2 if self.taps > 1 else 1
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
+        from .. import ops
+        b = bindings_of(cache, self.n_needs)
+        pages = b[0]
+        conv_state = b[1].state if self.taps > 1 else None
+        proj = self.qkv(x, out_dtype=torch.float32)
+        q = ops.sink_attn_prep(proj, 0, self.bias, self.conv_w, self.taps, conv_state, self.q_norm_w, self.k_norm_w,
+                               float(self.eps or 0.0), self.qk_freq, self.rot, self.v_freq, self.interleaved, ctx, pages,
+                               self.nh, self.nkv, self.hd, self.vd, self.dtype)
+        if conv_state is not None:
+            ops.conv_state_update(conv_state, proj, 0, self.bias, self.taps, ctx)
+        o = ops.attention_plain_sink(q, pages, ctx, self.nh, self.nkv, self.hd, self.vd, self.scale, self.window, self.sinks,
+                                     self.v_freq, self.interleaved)
+        return self.out_proj(o, out_dtype=torch.float32 if self.out32 else None)
+
+
+register_mixer("sink_attention", SinkAttentionMixer)

@@ -321,7 +321,8 @@ class Program:
             pending = self._view(regs.pending, (T, H), self.dtype) if regs.pending else None
             n_y = T if regs.phase != 2 else int(rows.numel())
             if role == "embedding":
-                x.copy_(part.forward(ctx.token_ids, ctx))
+                item = getattr(part, "cache_item", None)      # an embedding that keeps something per request
+                x.copy_(part.forward(ctx.token_ids, ctx) if item is None else part.forward(ctx.token_ids, ctx, bindings[item]))
             elif role in ("norm", "block"):
                 res = Residual(x)
                 res.pending = pending

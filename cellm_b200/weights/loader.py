@@ -86,6 +86,12 @@ def _convert(t: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     raise WeightError(f"element type {t.dtype} cannot be used")
 
 
+def _shape_fits(got, want) -> bool:
+    """Whether a file tensor's shape is the declared one; a declared extent of -1 takes any (a size that only the
+    file gives, such as the rank of a low-rank product)."""
+    return len(got) == len(want) and all(w == -1 or g == w for g, w in zip(got, want))
+
+
 def load_weights(folder: str, plan: ModelPlan, dtype: torch.dtype, device) -> dict[str, torch.Tensor]:
     files = _open_files(folder)
     where: dict[str, SafetensorsFile] = {}
@@ -94,14 +100,14 @@ def load_weights(folder: str, plan: ModelPlan, dtype: torch.dtype, device) -> di
             where[name] = f
     want = expected_tensors(plan)
     missing = sorted(n for n in want if n not in where)
-    unexpected = sorted(n for n in where if n not in want)
+    unexpected = sorted(n for n in where if n not in want and n not in plan.unread_tensors)
     wrong_shape, wrong_dtype = [], []
     for name, ts in want.items():
         f = where.get(name)
         if f is None:
             continue
         e = f.entries[name]
-        if tuple(e.shape) != tuple(ts.shape):
+        if not _shape_fits(e.shape, ts.shape):
             wrong_shape.append((name, tuple(e.shape), tuple(ts.shape)))
         if not e.dtype.is_floating_point or e.dtype == torch.float64:
             wrong_dtype.append((name, str(e.dtype)))

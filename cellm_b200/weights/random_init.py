@@ -16,6 +16,7 @@ from dataclasses import dataclass
 import torch
 
 from ..config.engine_config import parse_dtype
+from ..config.errors import ConfigError
 from ..config.registry import config_from_dict
 from .loader import expected_tensors
 from .safetensors_io import save_file
@@ -28,6 +29,8 @@ class InitSpec:
     conv_tap_std: float = 0.1
     bias_std: float = 0.02
     norm_jitter: float = 0.1
+    conv_tap_wide_std: float = 0.5      # taps of a convolution whose output is the layer's signal itself
+    sink_std: float = 1.0
 
 
 def _generator(seed: int, name: str) -> torch.Generator:
@@ -43,8 +46,14 @@ def random_tensor(name: str, shape, init: str, seed: int, spec: InitSpec) -> tor
         return 1.0 + (torch.rand(shape, generator=g, dtype=torch.float32) * 2.0 - 1.0) * spec.norm_jitter
     if init == "norm_offset":
         return (torch.rand(shape, generator=g, dtype=torch.float32) * 2.0 - 1.0) * spec.norm_jitter
+    if init == "unit_interval":         # a lower bound of a gate: inside (0, 1)
+        return 0.05 + 0.6 * torch.rand(shape, generator=g, dtype=torch.float32)
+    if init == "log_rate":              # the logarithm of a decay's rate
+        return torch.log(0.5 + 3.5 * torch.rand(shape, generator=g, dtype=torch.float32))
+    if init == "linear_wide":           # the second matrix of a low-rank product: its input is small
+        return torch.randn(shape, generator=g, dtype=torch.float32) * (1.0 / max(1, shape[-1]) ** 0.5)
     std = {"linear": spec.linear_std, "embedding": spec.embedding_std, "conv_tap": spec.conv_tap_std,
-           "bias": spec.bias_std}[init]
+           "conv_tap_wide": spec.conv_tap_wide_std, "bias": spec.bias_std, "sink": spec.sink_std}[init]
     return torch.randn(shape, generator=g, dtype=torch.float32) * std
 
 
@@ -56,6 +65,8 @@ def write_random_model(folder: str, config: dict, seed: int = 0, dtype="bfloat16
     cfg, plan = config_from_dict(config)
     tensors = {}
     for name, ts in expected_tensors(plan).items():
+        if any(n < 0 for n in ts.shape):
+            raise ConfigError(f"random weights: the configuration does not give every size of {name!r} {list(ts.shape)}")
         tensors[name] = random_tensor(name, ts.shape, ts.init, seed, init).to(store)
     os.makedirs(folder, exist_ok=True)
     with open(os.path.join(folder, "config.json"), "w") as f:
