@@ -34,6 +34,7 @@ attention_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part
                        const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ cu_seqlens,
                        const int* __restrict__ ctx_lens, const int* __restrict__ block_table, int bt_stride,
                        int B, int T, int num_pages, int page_size, int nh, int nkv, float scale_log2e, int window,
+                       const float* __restrict__ sinks, const float* __restrict__ unrot, int interleaved,
                        int* __restrict__ err) {
     constexpr int BM = 16 * NWARPS, BN = FA_BN, CH = HD / 8, NT = HD / 8, THREADS = NWARPS * 32;
     extern __shared__ __align__(128) uint8_t fa_smem[];
@@ -218,7 +219,56 @@ attention_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part
     l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
     const int col = (lane & 3) * 2;
     if (nsplit == 1) {
+        if (sinks) {
+            // a sink: one more term exp(sink_h) in the row's denominator, with no key and no value
+            if (row_a < rows) l_a += exp2f(sinks[kvh * G + row_a % G] * 1.4426950408889634f - (m_a == -INFINITY ? 0.f : m_a));
+            if (row_b < rows) l_b += exp2f(sinks[kvh * G + row_b % G] * 1.4426950408889634f - (m_b == -INFINITY ? 0.f : m_b));
+        }
         const float inv_a = l_a > 0.f ? 1.0f / l_a : 0.f, inv_b = l_b > 0.f ? 1.0f / l_b : 0.f;
+        if (unrot) {
+            // values were cached turned by their own positions: a row's sum is turned back by the row's position
+#pragma unroll
+            for (int n = 0; n < NT; ++n) { o[n][0] *= inv_a; o[n][1] *= inv_a; o[n][2] *= inv_b; o[n][3] *= inv_b; }
+            if (interleaved) {
+#pragma unroll
+                for (int n = 0; n < NT; ++n) {
+                    const int mm = (n * 8 + col) >> 1;
+                    float c, sn;
+                    split_sincos((float)pos_a, unrot[2 * mm], unrot[2 * mm + 1], &c, &sn);
+                    float u = o[n][0], v = o[n][1];
+                    o[n][0] = u * c + v * sn; o[n][1] = v * c - u * sn;
+                    split_sincos((float)pos_b, unrot[2 * mm], unrot[2 * mm + 1], &c, &sn);
+                    u = o[n][2]; v = o[n][3];
+                    o[n][2] = u * c + v * sn; o[n][3] = v * c - u * sn;
+                }
+            } else {
+#pragma unroll
+                for (int n = 0; n < NT / 2; ++n) {
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int mm = n * 8 + col + e;
+                        float c, sn;
+                        split_sincos((float)pos_a, unrot[2 * mm], unrot[2 * mm + 1], &c, &sn);
+                        float u = o[n][e], v = o[n + NT / 2][e];
+                        o[n][e] = u * c + v * sn; o[n + NT / 2][e] = v * c - u * sn;
+                        split_sincos((float)pos_b, unrot[2 * mm], unrot[2 * mm + 1], &c, &sn);
+                        u = o[n][2 + e]; v = o[n + NT / 2][2 + e];
+                        o[n][2 + e] = u * c + v * sn; o[n + NT / 2][2 + e] = v * c - u * sn;
+                    }
+                }
+            }
+            if (row_a < rows) {
+                __nv_bfloat16* dst = out + (size_t)(t_base + row_a / G) * nh * HD + (size_t)(kvh * G + row_a % G) * HD + col;
+#pragma unroll
+                for (int n = 0; n < NT; ++n) *reinterpret_cast<uint32_t*>(dst + n * 8) = pack_bf16(o[n][0], o[n][1]);
+            }
+            if (row_b < rows) {
+                __nv_bfloat16* dst = out + (size_t)(t_base + row_b / G) * nh * HD + (size_t)(kvh * G + row_b % G) * HD + col;
+#pragma unroll
+                for (int n = 0; n < NT; ++n) *reinterpret_cast<uint32_t*>(dst + n * 8) = pack_bf16(o[n][2], o[n][3]);
+            }
+            return;
+        }
         if (row_a < rows) {
             __nv_bfloat16* dst = out + (size_t)(t_base + row_a / G) * nh * HD + (size_t)(kvh * G + row_a % G) * HD + col;
 #pragma unroll
@@ -250,7 +300,9 @@ attention_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part
 
 // out[row] = sum_s 2^(m_s - m) O_s / sum_s 2^(m_s - m) l_s, pieces in order.
 __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o,
-                                       const float* __restrict__ part_ml, size_t n_rows, int hd, int nsplit) {
+                                       const float* __restrict__ part_ml, size_t n_rows, int hd, int nsplit,
+                                       const float* __restrict__ sinks, const float* __restrict__ unrot,
+                                       int interleaved, const int* __restrict__ positions, int nh) {
     pdl_trigger();
     pdl_wait();
     const size_t row = blockIdx.x;
@@ -260,7 +312,29 @@ __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const fl
     float l = 0.f;
     for (int s = 0; s < nsplit; ++s)
         l += exp2f(part_ml[((size_t)s * n_rows + row) * 2] - use) * part_ml[((size_t)s * n_rows + row) * 2 + 1];
+    if (sinks) l += exp2f(sinks[row % nh] * 1.4426950408889634f - use);
     const float inv = l > 0.f ? 1.0f / l : 0.f;
+    if (unrot) {
+        // a thread a pair: the merged sum is turned back by the row's position
+        const float fp = (float)positions[row / nh];
+        for (int mm = threadIdx.x; mm < hd / 2; mm += blockDim.x) {
+            const int d0 = interleaved ? 2 * mm : mm, d1 = interleaved ? 2 * mm + 1 : mm + hd / 2;
+            float u = 0.f, v = 0.f;
+            for (int s = 0; s < nsplit; ++s) {
+                const float w = exp2f(part_ml[((size_t)s * n_rows + row) * 2] - use);
+                if (w != 0.f) {
+                    u += w * part_o[((size_t)s * n_rows + row) * hd + d0];
+                    v += w * part_o[((size_t)s * n_rows + row) * hd + d1];
+                }
+            }
+            u *= inv; v *= inv;
+            float c, sn;
+            split_sincos(fp, unrot[2 * mm], unrot[2 * mm + 1], &c, &sn);
+            out[row * hd + d0] = __float2bfloat16_rn(u * c + v * sn);
+            out[row * hd + d1] = __float2bfloat16_rn(v * c - u * sn);
+        }
+        return;
+    }
     for (int d = threadIdx.x; d < hd; d += blockDim.x) {
         float acc = 0.f;
         for (int s = 0; s < nsplit; ++s) {
@@ -275,7 +349,7 @@ template <int HD, int NWARPS>
 int launch_flash(__nv_bfloat16* out, float* part_o, float* part_ml, const __nv_bfloat16* q, const __nv_bfloat16* k_pool,
                  const __nv_bfloat16* v_pool, const int* cu, const int* ctx, const int* bt, int bt_stride, int B, int T,
                  int n_tiles, int num_pages, int page_size, int nh, int nkv, float scale, int window, int nsplit,
-                 int* err, cudaStream_t stream) {
+                 int* err, cudaStream_t stream, const float* sinks = nullptr, const float* unrot = nullptr, int interleaved = 0) {
     constexpr int BM = 16 * NWARPS;
     const size_t smem = (size_t)(BM + 4 * FA_BN) * HD * 2;
     static bool configured = false;
@@ -287,7 +361,7 @@ int launch_flash(__nv_bfloat16* out, float* part_o, float* part_ml, const __nv_b
     dim3 grid((unsigned)n_tiles, (unsigned)nkv, (unsigned)nsplit);
     CELLM_RUN((attention_flash_kernel<HD, NWARPS>), grid, NWARPS * 32, smem, stream,
               out, part_o, part_ml, q, k_pool, v_pool, cu, ctx, bt, bt_stride, B, T, num_pages, page_size, nh, nkv,
-              scale * 1.4426950408889634f, window, err);
+              scale * 1.4426950408889634f, window, sinks, unrot, interleaved, err);
     return CELLM_OK;
 }
 
@@ -299,12 +373,14 @@ CELLM_API int cellm_attention_flash_supports(int hd) { return hd == 32 || hd == 
 // out, q: [T, nh*hd] bf16. n_tiles: sum over requests of ceil(q_len * (nh/nkv) / rows_per_cta),
 // rows_per_cta = 64 (wide = 1) or 16 (wide = 0). nsplit > 1 needs part_o
 // [nsplit, T*nh, hd] and part_ml [nsplit, T*nh, 2] floats.
-CELLM_API int cellm_attention_flash(void* out, float* part_o, float* part_ml, const void* q, const void* k_pool,
-                                    const void* v_pool, const int* cu_seqlens, const int* ctx_lens,
-                                    const int* block_table, int bt_stride, int B, int T, int n_tiles, int num_pages,
-                                    int page_size, int nh, int nkv, int hd, float scale, int window, int wide,
-                                    int nsplit, int* err, cudaStream_t stream) {
+static int attention_flash_impl(void* out, float* part_o, float* part_ml, const void* q, const void* k_pool,
+                                const void* v_pool, const int* cu_seqlens, const int* ctx_lens,
+                                const int* block_table, int bt_stride, int B, int T, int n_tiles, int num_pages,
+                                int page_size, int nh, int nkv, int hd, float scale, int window, int wide,
+                                int nsplit, int* err, cudaStream_t stream, const float* sinks, const float* unrot,
+                                int interleaved, const int* positions) {
     if (T <= 0 || n_tiles <= 0) return CELLM_OK;
+    if (unrot && nsplit > 1 && !positions) return CELLM_ERR_ARG;
     if (nkv <= 0 || nh % nkv) return CELLM_ERR_SIZE;
     if (nsplit < 1 || (nsplit > 1 && (!part_o || !part_ml))) return CELLM_ERR_ARG;
     if (nkv > 65535 || nsplit > 65535) return CELLM_ERR_SIZE;
@@ -313,11 +389,11 @@ CELLM_API int cellm_attention_flash(void* out, float* part_o, float* part_ml, co
     rc = wide ? launch_flash<HD_, 4>((__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q,               \
                                      (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, cu_seqlens,      \
                                      ctx_lens, block_table, bt_stride, B, T, n_tiles, num_pages, page_size, nh,   \
-                                     nkv, scale, window, nsplit, err, stream)                                     \
+                                     nkv, scale, window, nsplit, err, stream, sinks, unrot, interleaved)          \
               : launch_flash<HD_, 1>((__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q,               \
                                      (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, cu_seqlens,      \
                                      ctx_lens, block_table, bt_stride, B, T, n_tiles, num_pages, page_size, nh,   \
-                                     nkv, scale, window, nsplit, err, stream)
+                                     nkv, scale, window, nsplit, err, stream, sinks, unrot, interleaved)
     if (hd == 32) GO(32);
     else if (hd == 64) GO(64);
     else if (hd == 128) GO(128);
@@ -326,9 +402,35 @@ CELLM_API int cellm_attention_flash(void* out, float* part_o, float* part_ml, co
     if (rc != CELLM_OK) return rc;
     if (nsplit > 1) {
         CELLM_RUN(attention_merge_kernel, (unsigned)((size_t)T * nh), hd >= 64 ? 64 : 32, 0, stream,
-                  (__nv_bfloat16*)out, (const float*)part_o, (const float*)part_ml, (size_t)T * nh, hd, nsplit);
+                  (__nv_bfloat16*)out, (const float*)part_o, (const float*)part_ml, (size_t)T * nh, hd, nsplit, sinks, unrot,
+                  interleaved, positions, nh);
     }
     return CELLM_OK;
+}
+
+CELLM_API int cellm_attention_flash(void* out, float* part_o, float* part_ml, const void* q, const void* k_pool,
+                                    const void* v_pool, const int* cu_seqlens, const int* ctx_lens,
+                                    const int* block_table, int bt_stride, int B, int T, int n_tiles, int num_pages,
+                                    int page_size, int nh, int nkv, int hd, float scale, int window, int wide,
+                                    int nsplit, int* err, cudaStream_t stream) {
+    return attention_flash_impl(out, part_o, part_ml, q, k_pool, v_pool, cu_seqlens, ctx_lens, block_table, bt_stride, B, T,
+                                n_tiles, num_pages, page_size, nh, nkv, hd, scale, window, wide, nsplit, err, stream, nullptr,
+                                nullptr, 0, nullptr);
+}
+
+// The same with a learned sink per head in every row's denominator (`sinks` [nh], 32-bit; null: none) and with the
+// rows' sums turned back by the rows' positions (`unrot` [hd/2][2]: the values' frequencies, high part and
+// remainder; null: values were cached unrotated; `interleaved`: pairs (2m, 2m + 1), else (m, m + hd/2)).
+// `positions` [T]: needed when the keys are cut into pieces.
+CELLM_API int cellm_attention_flash_sink(void* out, float* part_o, float* part_ml, const void* q, const void* k_pool,
+                                         const void* v_pool, const int* cu_seqlens, const int* ctx_lens,
+                                         const int* block_table, int bt_stride, int B, int T, int n_tiles, int num_pages,
+                                         int page_size, int nh, int nkv, int hd, float scale, int window, int wide,
+                                         int nsplit, const float* sinks, const float* unrot, int interleaved,
+                                         const int* positions, int* err, cudaStream_t stream) {
+    return attention_flash_impl(out, part_o, part_ml, q, k_pool, v_pool, cu_seqlens, ctx_lens, block_table, bt_stride, B, T,
+                                n_tiles, num_pages, page_size, nh, nkv, hd, scale, window, wide, nsplit, err, stream, sinks,
+                                unrot, interleaved, positions);
 }
 
 // ---------------------------------------------------------------------------

@@ -40,6 +40,18 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(f
     return __float2bfloat16_rn(v);
 }
 
+// cos and sin of fp * (hi + lo): the angle of a position times a frequency that was made in 64-bit and is given as
+// its nearest float and the remainder, so that the product keeps its low bits.
+__device__ __forceinline__ void split_sincos(float fp, float hi, float lo, float* c_out, float* s_out) {
+    const float a = fp * hi;
+    const float e = fmaf(fp, hi, -a) + fp * lo;
+    float s, c, se, ce;
+    sincosf(a, &s, &c);
+    sincosf(e, &se, &ce);
+    *c_out = c * ce - s * se;
+    *s_out = s * ce + c * se;
+}
+
 // Activations by number: 0 gelu (exact), 1 gelu (tanh form), 2 silu, 3 relu, 4 the square of relu.
 __device__ __forceinline__ float cellm_activate(float z, int act) {
     switch (act) {

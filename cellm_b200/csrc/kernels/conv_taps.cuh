@@ -5,7 +5,7 @@
 #pragma once
 #include "common.cuh"
 
-#define CONV_TAPS_MAX 8
+#define CONV_TAPS_MAX 16
 
 struct ConvTaps {
     const float* proj;      // [T, ld]: the step's projections, 32-bit

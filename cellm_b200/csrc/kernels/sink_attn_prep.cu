@@ -11,16 +11,6 @@
 // All arithmetic is 32-bit; angles are pos * (hi + lo) in split arithmetic from tables made in 64-bit.
 #include "conv_taps.cuh"
 
-__device__ __forceinline__ void split_sincos(float fp, float hi, float lo, float* c_out, float* s_out) {
-    const float a = fp * hi;
-    const float e = fmaf(fp, hi, -a) + fp * lo;
-    float s, c, se, ce;
-    sincosf(a, &s, &c);
-    sincosf(e, &se, &ce);
-    *c_out = c * ce - s * se;
-    *s_out = s * ce + c * se;
-}
-
 template <typename TA>
 __global__ void __launch_bounds__(256)
 sink_attn_prep_kernel(TA* __restrict__ q_out, TA* __restrict__ k_pool, TA* __restrict__ v_pool, ConvTaps cv,

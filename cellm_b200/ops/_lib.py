@@ -72,6 +72,7 @@ _SIGNATURES = {
     "attention_flash": {
         "cellm_attention_flash": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, I, P, P],
         "cellm_attention_flash_supports": [I],
+        "cellm_attention_flash_sink": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, I, P, P, I, P, P, P],
     },
     "attention_latent": {
         "cellm_attention_latent": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P],

@@ -114,6 +114,35 @@ def attention_plain_sink(q: torch.Tensor, cache, ctx, nh: int, nkv: int, hd: int
     return out
 
 
+def attention_flash_sink(q: torch.Tensor, cache, ctx, nh: int, nkv: int, hd: int, scale: float, window: int,
+                         sinks: Optional[torch.Tensor], unrot: Optional[torch.Tensor], interleaved: bool) -> torch.Tensor:
+    """The same attention on the tensor cores (bfloat16; keys and values of one width hd of 32, 64 or 128): tiles of
+    64 (token, head) rows for prompt portions, of 16 for steps of single tokens, whose keys are cut into pieces when
+    the tiles alone leave most of the GPU idle."""
+    _f32(sinks, unrot)
+    k, v, bt = cache.k, cache.v, cache.block_table
+    if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.shape != k.shape or hd not in (32, 64, 128):
+        raise ValueError("attention_flash_sink: bfloat16 and keys and values of one width of 32, 64 or 128")
+    T, G = q.shape[0], nh // nkv
+    wide = ctx.max_q_len * G > 16
+    rows = 64 if wide else 16
+    n_tiles = sum(-(-n * G // rows) for n in ctx.q_lens)
+    # pieces of keys: only where a step's tiles are few; a piece is at least two blocks of 64 keys
+    longest = ctx.max_total_len          # a captured step's bound: the width of its block tables
+    span = min(longest, window + ctx.max_q_len) if window > 0 else longest
+    nsplit = max(1, min(-(-span // 128), 296 // max(1, n_tiles * nkv), 32))
+    out = torch.empty((T, nh * hd), dtype=q.dtype, device=q.device)
+    part_o = part_ml = None
+    if nsplit > 1:
+        part_o = torch.empty((nsplit, T * nh, hd), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((nsplit, T * nh, 2), dtype=torch.float32, device=q.device)
+    check(fn("attention_flash", "cellm_attention_flash_sink")(
+        ptr(out), ptr(part_o), ptr(part_ml), ptr(q), ptr(k), ptr(v), ptr(ctx.cu_seqlens), ptr(ctx.ctx_lens), ptr(bt), bt.stride(0),
+        ctx.B, T, n_tiles, k.shape[0], cache.page_size, nh, nkv, hd, float(scale), int(window), int(wide), nsplit, ptr(sinks), ptr(unrot),
+        int(interleaved), ptr(ctx.positions), ptr(ctx.err), stream_of(q)), "attention_flash_sink")
+    return out
+
+
 def hgrn2_scan(proj: torch.Tensor, col_q: int, col_f: int, col_v: int, f_bias: torch.Tensor, lower: torch.Tensor, state: torch.Tensor,
                ctx, heads: int, dim: int, vd: int) -> torch.Tensor:
     """The HGRN2 recurrence over every request's tokens of the step; state [slots, heads, dim, vd] float32 is moved on.

@@ -15,8 +15,10 @@ Scores, softmax, norms, angles and the convolutions' sums are 32-bit. The reques
 in its state slot, so a sequence cut anywhere sees the same convolution inputs.
 
 Kernels: one product for q | k | v with 32-bit sums, `sink_attn_prep` (bias, convolution, norm, rotations, cache
-write), `conv_state_update`, the attention itself (32-bit: the plain kernel with sink and turn-back; bfloat16: the
-same kernel), the output product."""
+write), `conv_state_update`, the attention itself (32-bit, and heads whose key and value widths differ or are none
+of 32, 64, 128: the plain kernel with sink and turn-back; bfloat16: the paged mma.sync flash kernel, which takes the
+sink into a row's denominator and turns the row's sum back in its epilogue, or in the merge of its pieces), the
+output product."""
 from __future__ import annotations
 
 import torch
@@ -27,6 +29,10 @@ from .base import CacheBinding, FixedState, Mixer, PagedKV, StepContext, TensorS
 from .linear import Linear, stack_rows
 from .registry import part_class, register_mixer
 from .rope import split_inv_freq
+
+
+# Tests turn the tensor-core attention off to compare it with the plain kernel on the same cache.
+OPTIONS = {"tensor_cores": True}
 
 
 def bindings_of(cache: CacheBinding, n: int) -> tuple:
@@ -128,8 +134,12 @@ class SinkAttentionMixer(Mixer):
                                self.nh, self.nkv, self.hd, self.vd, self.dtype)
         if conv_state is not None:
             ops.conv_state_update(conv_state, proj, 0, self.bias, self.taps, ctx)
-        o = ops.attention_plain_sink(q, pages, ctx, self.nh, self.nkv, self.hd, self.vd, self.scale, self.window, self.sinks,
-                                     self.v_freq, self.interleaved)
+        if self.dtype == torch.bfloat16 and self.hd == self.vd and self.hd in (32, 64, 128) and OPTIONS["tensor_cores"]:
+            o = ops.attention_flash_sink(q, pages, ctx, self.nh, self.nkv, self.hd, self.scale, self.window, self.sinks,
+                                         self.v_freq, self.interleaved)
+        else:
+            o = ops.attention_plain_sink(q, pages, ctx, self.nh, self.nkv, self.hd, self.vd, self.scale, self.window, self.sinks,
+                                         self.v_freq, self.interleaved)
         return self.out_proj(o, out_dtype=torch.float32 if self.out32 else None)
 
 

@@ -81,9 +81,9 @@ def rotate_interleaved(x, positions, freqs, sign=1.0):
     return out
 
 
-def sink_window_attention(q, k, v, scale, window, sinks):
-    """q [T, H, d], k [T, G, d], v [T, G, dv]; position i sees j with 0 <= i - j < window; the softmax's
-    denominator also holds exp(sink_h)."""
+def sink_window_attention(q, k, v, scale, window, sinks, weights_out=None):
+    """q [T, H, d], k [T, G, d], v [T, G, dv]; position i sees j with 0 <= i - j < window (None: every j <= i); the
+    softmax's denominator also holds exp(sink_h). `weights_out`, a list, receives every head's weights [T, T]."""
     T, H, d = q.shape
     G = k.shape[1]
     out = torch.zeros(T, H, v.shape[2], dtype=q.dtype)
@@ -92,16 +92,18 @@ def sink_window_attention(q, k, v, scale, window, sinks):
         s = (q[:, h] @ k[:, g].T) * scale
         i = torch.arange(T)[:, None]
         j = torch.arange(T)[None, :]
-        ok = (i - j >= 0) & (i - j < window)
+        ok = (i - j >= 0) & ((i - j < window) if window else (i >= j))
         s = s.masked_fill(~ok, -math.inf)
         m = torch.maximum(s.max(dim=1, keepdim=True).values, sinks[h].reshape(1, 1))
         e = torch.exp(s - m)
         den = e.sum(dim=1, keepdim=True) + torch.exp(sinks[h] - m)
         out[:, h] = (e / den) @ v[:, g]
+        if weights_out is not None:
+            weights_out.append(e / den)
     return out
 
 
-def left_mixer(h, m, w, p, eps):
+def left_mixer(h, m, w, p, eps, weights_out=None):
     """The windowed attention with sinks, short convolutions, a norm over the projection, rotated keys and values."""
     T = h.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
@@ -114,13 +116,15 @@ def left_mixer(h, m, w, p, eps):
     q = rms(q, eps) * w[p + "q.norm"]
     k = rms(k, eps) * w[p + "k.norm"]
     q, k, v = q.reshape(T, H, d), k.reshape(T, G, d), v.reshape(T, G, dv)
-    rot = m["rot"]
-    fr = scaled_frequencies(rot["base"], rot["dims"], rot.get("scaling"))
-    q, k = rotate_interleaved(q, pos, fr), rotate_interleaved(k, pos, fr)
-    fv = scaled_frequencies(rot["base"], dv, None)
-    v = rotate_interleaved(v, pos, fv)
-    o = sink_window_attention(q, k, v, m["scale"], m["mask"]["size"], w[p + "sink"])
-    o = rotate_interleaved(o, pos, fv, sign=-1.0)
+    rot = m.get("rot")
+    if rot is not None:
+        fr = scaled_frequencies(rot["base"], rot["dims"], rot.get("scaling"))
+        q, k = rotate_interleaved(q, pos, fr), rotate_interleaved(k, pos, fr)
+        fv = scaled_frequencies(rot["base"], dv, None)
+        v = rotate_interleaved(v, pos, fv)
+    o = sink_window_attention(q, k, v, m["scale"], (m.get("mask") or {}).get("size"), w[p + "sink"], weights_out)
+    if rot is not None:
+        o = rotate_interleaved(o, pos, fv, sign=-1.0)
     return o.reshape(T, H * dv) @ w[p + "o"].T
 
 
