@@ -10,9 +10,39 @@ import torch
 
 F64 = torch.float64
 
+# How sensitive a model's logits are to rounding differs from row to row (a head's read-out that nearly cancels is scaled
+# up by the norm behind it). `perturbed` multiplies every intermediate result by 1 + rel * u, u uniform in [-1, 1) and
+# drawn anew for every entry, which is what a 16-bit engine's roundings do to them; the difference from the exact run
+# measures, row by row, what rounding alone causes.
+_NOISE = None
+
+
+class perturbed:
+    def __init__(self, rel, seed):
+        self.rel, self.gen = rel, torch.Generator().manual_seed(seed)
+
+    def __enter__(self):
+        global _NOISE
+        _NOISE = self
+
+    def __exit__(self, *a):
+        global _NOISE
+        _NOISE = None
+
+
+def _p(x):
+    if _NOISE is None:
+        return x
+    return x * (1 + _NOISE.rel * (2 * torch.rand(x.shape, generator=_NOISE.gen, dtype=F64) - 1))
+
+
+def lin(h, W, b=None):
+    y = h @ W.T
+    return _p(y if b is None else y + b)
+
 
 def rms(x, eps):
-    return x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + eps)
+    return _p(x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + eps))
 
 
 def gelu_tanh(z):
@@ -47,7 +77,7 @@ def causal_conv(u, taps_w):
     y = torch.zeros_like(u)
     for j in range(taps):
         y = y + padded[j:j + T] * taps_w[:, j]
-    return y
+    return _p(y)
 
 
 def scaled_frequencies(base, dims, scaling):
@@ -78,7 +108,7 @@ def rotate_interleaved(x, positions, freqs, sign=1.0):
     u, v = x[..., 0:2 * n:2], x[..., 1:2 * n:2]
     out[..., 0:2 * n:2] = u * c - v * s
     out[..., 1:2 * n:2] = v * c + u * s
-    return out
+    return _p(out)
 
 
 def sink_window_attention(q, k, v, scale, window, sinks, weights_out=None):
@@ -100,7 +130,7 @@ def sink_window_attention(q, k, v, scale, window, sinks, weights_out=None):
         out[:, h] = (e / den) @ v[:, g]
         if weights_out is not None:
             weights_out.append(e / den)
-    return out
+    return _p(out)
 
 
 def left_mixer(h, m, w, p, eps, weights_out=None):
@@ -108,9 +138,7 @@ def left_mixer(h, m, w, p, eps, weights_out=None):
     T = h.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     pos = torch.arange(T)
-    q = h @ w[p + "q"].T + w[p + "q.b"]
-    k = h @ w[p + "k"].T + w[p + "k.b"]
-    v = h @ w[p + "v"].T + w[p + "v.b"]
+    q, k, v = lin(h, w[p + "q"], w[p + "q.b"]), lin(h, w[p + "k"], w[p + "k.b"]), lin(h, w[p + "v"], w[p + "v.b"])
     if m.get("conv"):
         q, k, v = causal_conv(q, w[p + "q.conv"]), causal_conv(k, w[p + "k.conv"]), causal_conv(v, w[p + "v.conv"])
     q = rms(q, eps) * w[p + "q.norm"]
@@ -125,30 +153,30 @@ def left_mixer(h, m, w, p, eps, weights_out=None):
     o = sink_window_attention(q, k, v, m["scale"], (m.get("mask") or {}).get("size"), w[p + "sink"], weights_out)
     if rot is not None:
         o = rotate_interleaved(o, pos, fv, sign=-1.0)
-    return o.reshape(T, H * dv) @ w[p + "o"].T
+    return lin(o.reshape(T, H * dv), w[p + "o"])
 
 
 def hgrn2(h, m, w, p, eps):
     """Linear attention whose forget gate also decides what is written."""
     T = h.shape[0]
     H, d, dv = m["heads"], m["dim"], m["vdim"]
-    q = torch.nn.functional.silu(h @ w[p + "q"].T).reshape(T, H, d)
-    v = (h @ w[p + "v"].T).reshape(T, H, dv)
+    q = torch.nn.functional.silu(lin(h, w[p + "q"])).reshape(T, H, d)
+    v = lin(h, w[p + "v"]).reshape(T, H, dv)
     low = w[p + "lower"]
-    f = (low + (1 - low) * torch.sigmoid(h @ w[p + "f"].T + w[p + "f.b"])).reshape(T, H, d)
+    f = (low + (1 - low) * torch.sigmoid(lin(h, w[p + "f"]) + w[p + "f.b"])).reshape(T, H, d)
     S = torch.zeros(H, d, dv, dtype=h.dtype)
     o = torch.zeros(T, H, dv, dtype=h.dtype)
     for t in range(T):
         S = f[t][:, :, None] * S + (1 - f[t])[:, :, None] * v[t][:, None, :]
         o[t] = torch.einsum("hdv,hd->hv", S, q[t])
-    o = rms(o, eps) * w[p + "norm"]
-    return o.reshape(T, H * dv) @ w[p + "o"].T
+    o = rms(_p(o), eps) * w[p + "norm"]
+    return lin(o.reshape(T, H * dv), w[p + "o"])
 
 
 def parallel_mixer(h, m, w, p, eps):
     a = left_mixer(h, m["left"], w, p + "left.", eps)
     b = hgrn2(h, m["right"], w, p + "right.", eps)
-    return 0.5 * (rms(a, eps) * w[p + "left.out"] + rms(b, eps) * w[p + "right.out"])
+    return _p(0.5 * (rms(a, eps) * w[p + "left.out"] + rms(b, eps) * w[p + "right.out"]))
 
 
 def channel_delta(h, m, w, p, eps):
@@ -156,15 +184,15 @@ def channel_delta(h, m, w, p, eps):
     T = h.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     silu = torch.nn.functional.silu
-    q = silu(causal_conv(h @ w[p + "q"].T, w[p + "q.conv"])).reshape(T, G, d)
-    k = silu(causal_conv(h @ w[p + "k"].T, w[p + "k.conv"])).reshape(T, G, d)
-    v = silu(causal_conv(h @ w[p + "v"].T, w[p + "v.conv"])).reshape(T, H, dv)
+    q = silu(causal_conv(lin(h, w[p + "q"]), w[p + "q.conv"])).reshape(T, G, d)
+    k = silu(causal_conv(lin(h, w[p + "k"]), w[p + "k.conv"])).reshape(T, G, d)
+    v = silu(causal_conv(lin(h, w[p + "v"]), w[p + "v.conv"])).reshape(T, H, dv)
     q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * d ** -0.5
     k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
-    beta = torch.sigmoid(h @ w[p + "b"].T)                                        # [T, H]
-    a = (h @ w[p + "a1"].T) @ w[p + "a2"].T + w[p + "dt_bias"]
+    beta = torch.sigmoid(lin(h, w[p + "b"]))                                      # [T, H]
+    a = lin(lin(h, w[p + "a1"]), w[p + "a2"]) + w[p + "dt_bias"]
     g = torch.exp(-torch.exp(w[p + "A_log"])[None, :, None] * torch.nn.functional.softplus(a).reshape(T, H, d))
-    gate = torch.sigmoid((h @ w[p + "g1"].T) @ w[p + "g2"].T).reshape(T, H, dv)
+    gate = torch.sigmoid(lin(lin(h, w[p + "g1"]), w[p + "g2"])).reshape(T, H, dv)
     S = torch.zeros(H, d, dv, dtype=h.dtype)
     o = torch.zeros(T, H, dv, dtype=h.dtype)
     rep = H // G
@@ -174,12 +202,12 @@ def channel_delta(h, m, w, p, eps):
         u = beta[t][:, None] * (v[t] - torch.einsum("hdv,hd->hv", S, kt))
         S = S + kt[:, :, None] * u[:, None, :]
         o[t] = torch.einsum("hdv,hd->hv", S, qt)
-    o = rms(o, eps) * w[p + "norm"] * gate
-    return o.reshape(T, H * dv) @ w[p + "o"].T
+    o = _p(rms(_p(o), eps) * w[p + "norm"] * gate)
+    return lin(o.reshape(T, H * dv), w[p + "o"])
 
 
 def dense_mlp(h, w, p):
-    return torch.relu(h @ w[p + "up"].T) ** 2 @ w[p + "down"].T
+    return lin(_p(torch.relu(lin(h, w[p + "up"])) ** 2), w[p + "down"])
 
 
 MIXERS = {"parallel": parallel_mixer, "channel_delta": channel_delta}
@@ -198,5 +226,5 @@ def forward(tokens, cfg, w, return_layers=False):
             y = y + dense_mlp(scalar_norm(x, w[p + "norm2"], eps), w, p + "mlp.")
         x = x + mult * y
         layers.append(x)
-    logits = scalar_norm(x, w["final.norm"], eps) @ w["head"].T
+    logits = lin(scalar_norm(x, w["final.norm"], eps), w["head"])
     return (logits, torch.stack(layers)) if return_layers else logits
