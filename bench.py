@@ -274,7 +274,7 @@ def step_matrices(model, tokens: int):
 
 def design_shapes(design: str) -> dict:
     from cellm_b200.config import presets
-    return {"vezalorn": presets.VEZALORN_SHAPES, "tufadra": presets.TUFADRA_SHAPES}[design]
+    return {"vezalorn": presets.VEZALORN_SHAPES, "tufadra": presets.TUFADRA_SHAPES, "padadra": presets.PADADRA_SHAPES}[design]
 
 
 def compare_designs(args, rng) -> int:
@@ -329,7 +329,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 runs")
-    ap.add_argument("--design", default=None, choices=["vezalorn", "tufadra"],
+    ap.add_argument("--design", default=None, choices=["vezalorn", "tufadra", "padadra"],
                     help="instead of the default workload: prefill and decode throughput of this design at a few sizes, "
                          "beside LFM2 at equal width, depth and feed-forward (random weights); prints one JSON line")
     ap.add_argument("--sizes", default="700m,1.2b", help="with --design: which of the shapes to run")

@@ -73,3 +73,27 @@ TUFADRA_SHAPES = {
     "1.2b": (_tufadra(2048, 16, 32, 8, 64, 6, 1024, 2048), "lfm2-1.2b"),
     "700m": (_tufadra(1536, 16, 24, 8, 64, 6, 896, 1536), "lfm2-700m"),
 }
+
+
+# ---- Padadra shapes beside LFM2's ----------------------------------------------------------------------------------
+def _padadra(width: int, layers: int, parallel_at, heads: int, kv_heads: int, rec_heads: int, ff: int, vocab: int = 65536) -> dict:
+    """Layers of a width and count that an LFM2 shape has: the two mixers side by side (LFM2's attention heads of 64 with
+    a window of 1,024 and convolutions of four taps, beside an HGRN2 recurrence with states of 64 x 128 a head) where
+    LFM2 has attention, the gated delta rule with states of 128 x 128 a head where it has its short convolutions, and a
+    feed-forward of LFM2's width beside every mixer."""
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 64, "scale": 0.125, "conv": 4, "mask": {"size": 1024},
+            "rot": {"base": 1000000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    right = {"heads": rec_heads, "dim": 64, "vdim": 128}
+    delta = {"heads": rec_heads, "kv_heads": rec_heads // 2, "dim": 128, "vdim": 128, "conv": 4, "decay_rank": 64, "gate_rank": 64}
+    mlp = {"kind": "dense", "ff": ff}
+    return {"architecture": "Padadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+            "embedding": {"scale": 1.0, "bigram": {"buckets": 100003, "mul_prev": 31, "mul_cur": 7}},
+            "layers": [{"type": "parallel", "mixer": {"left": dict(left), "right": dict(right)}, "mlp": dict(mlp)} if i in parallel_at else
+                       {"type": "channel_delta", "mixer": dict(delta), "mlp": dict(mlp)} for i in range(layers)]}
+
+
+# name -> (Padadra shape, the LFM2 shape of equal width, depth, feed-forward and attention places)
+PADADRA_SHAPES = {
+    "1.2b": (_padadra(2048, 16, [2, 5, 8, 10, 12, 14], 32, 8, 16, 8192), "lfm2-1.2b"),
+    "700m": (_padadra(1536, 16, [2, 5, 8, 10, 12, 14], 24, 8, 12, 6912), "lfm2-700m"),
+}

@@ -1031,7 +1031,7 @@ CELLM_API int cellm_gemm_grouped_tcgen05(void* C, const void* A, const void* W, 
     if (K <= 0 || (K & 7) || groups < 1 || (tile_group && (M % BM)) || (!tile_group && groups != 1)) return CELLM_ERR_SIZE;
     if (((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ((lda * 2) & 15) || ((ldw * 2) & 15)) return CELLM_ERR_ALIGN;
     if (out_dtype != CELLM_F32 && out_dtype != CELLM_BF16) return CELLM_ERR_DTYPE;
-    if (act > 3) return CELLM_ERR_ARG;
+    if (act > 4) return CELLM_ERR_ARG;
     const int bn = N > 128 ? 256 : 128;
     CUtensorMap map_a, map_w;
     if (!tensor_map(&map_a, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, (uint32_t)BM)) return CELLM_ERR_ARG;

@@ -3,16 +3,179 @@
 //   HGRN2            S <- diag(f) S + (1 - f) v^T                      o = S^T q
 //   gated delta rule S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
 //
-// In both, column j of S needs only v_j (and the token's vectors over the rows), so a thread owns a column and a
-// warp 32 neighbouring columns of one (request, head); it walks the request's tokens of the step in order, from the
-// state the step before left. The walk is the same however the sequence was cut, so the state after a token is
-// bit-identical. Everything that enters the recurrence is 32-bit: the projections come as 32-bit sums.
+// In both, column j of S needs only v_j (and the token's vectors over the rows), so the columns are independent: a
+// block walks some neighbouring columns of one (request, head) through the request's tokens of the step in order,
+// from the state the step before left. The walk and the order of every sum depend on the head's sizes alone, not on
+// how the sequence was cut, so the state after a token is bit-identical. Everything that enters the recurrence is
+// 32-bit: the projections come as 32-bit sums. Heads of more than 128 rows keep a warp's 32 columns in shared memory
+// (`*_scan_kernel`); the others live in registers (`*_walk_kernel`).
 //
 // Also here: the update of a short convolution's state (conv_taps.cuh), the preparation of the delta rule's
 // inputs (convolution + silu, unit vectors, beta, decays), and the norm over a head's output with an optional gate.
 #include "conv_taps.cuh"
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
+
+// ------------------------------------------------------------------------------------------------ the walk
+// Heads of up to 128 rows: a column of S is shared by RG neighbouring lanes, each holding DIM / RG of its rows in
+// registers (rows in groups of four, dealt round robin to the lanes, so that a lane's 16-byte reads of the token's
+// vectors in shared memory fall into different banks), and a block of four warps walks 128 / RG neighbouring columns
+// of one (request, head). The tokens' vectors over the rows, the block's entries of v and beta come in chunks of
+// eight tokens through asynchronous copies into three stages of shared memory, two chunks ahead of the one in use:
+// a chunk costs one barrier and no wait for memory, and within a chunk the warps run free. Sums over a column's rows
+// are added lane by lane (shuffles) in a fixed order. DIM is the next of 16, 32, 64, 128 above the head's rows; the
+// rows beyond are zeros that nothing reads back.
+template <int DIM> struct WalkShape {
+    static constexpr int RG = DIM >= 64 ? 8 : (DIM == 32 ? 4 : 2);
+    static constexpr int ROWS = DIM / RG;          // rows of a column in one lane: 16 or 8
+    static constexpr int CPW = 32 / RG;            // columns a warp
+    static constexpr int CPB = 4 * CPW;            // columns a block
+};
+#define WALK_THREADS 128
+#define WALK_CHUNK 8
+#define WALK_STAGES 3
+
+template <int RG> __device__ __forceinline__ float sum_over_rows(float x) {
+#pragma unroll
+    for (int d = 1; d < RG; d <<= 1) x += __shfl_xor_sync(0xffffffffu, x, d);
+    return x;
+}
+
+__device__ __forceinline__ void copy_async4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copy_async16(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Where the vectors over a head's rows lie: array a of token t and head h starts at p[a] + t * ld[a] + (h / heads_per[a]) * dim.
+// Delta rule: q, k, decay. HGRN2: q, f.
+struct WalkVectors {
+    const float* p[3];
+    long long ld[3];
+    int heads_per[3];
+    int vec16;          // every start is a multiple of 16 bytes: copies of four values
+};
+
+template <int DIM, bool DELTA>
+__global__ void __launch_bounds__(WALK_THREADS)
+state_walk_kernel(float* __restrict__ o_out, float* __restrict__ state, long long slot_stride, int n_slots, const WalkVectors vec,
+                  const float* __restrict__ v_in, long long ld_v, const float* __restrict__ beta,
+                  const int* __restrict__ cu_seqlens, const int* __restrict__ slot_ids, int heads, int dim, int vd,
+                  int* __restrict__ err) {
+    using W = WalkShape<DIM>;
+    constexpr int RG = W::RG, ROWS = W::ROWS, CPB = W::CPB, NV = DELTA ? 3 : 2;
+    constexpr int TOK = NV * DIM + CPB + 4;          // a token in a stage: its vectors | the block's entries of v | beta
+    __shared__ __align__(16) float buf[WALK_STAGES][WALK_CHUNK * TOK];
+    const int b = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int r = lane % RG, cl = warp * W::CPW + lane / RG, col0 = blockIdx.z * CPB, j = col0 + cl;
+    pdl_trigger();
+    pdl_wait();
+    const int slot = slot_ids[b];
+    if (slot < 0 || slot >= n_slots) { if (tid == 0) atomicOr(err, CELLM_DEV_BAD_SLOT); return; }
+    const int start = cu_seqlens[b], end = cu_seqlens[b + 1];
+    if (end <= start) return;
+    float* st = state + (size_t)slot * slot_stride + (size_t)h * dim * vd;
+    const bool live = j < vd;
+    if (dim < DIM) {            // the rows beyond the head's own stay zero in every stage
+        for (int i = tid; i < WALK_STAGES * WALK_CHUNK * TOK; i += WALK_THREADS) (&buf[0][0])[i] = 0.f;
+        __syncthreads();
+    }
+    const int n_chunks = (end - start + WALK_CHUNK - 1) / WALK_CHUNK;
+    auto issue = [&](int c) {
+        float* dst = buf[c % WALK_STAGES];
+        const int t0 = start + c * WALK_CHUNK, nt = min(WALK_CHUNK, end - t0);
+#pragma unroll
+        for (int a = 0; a < NV; ++a) {
+            const float* src = vec.p[a] + (size_t)t0 * vec.ld[a] + (h / vec.heads_per[a]) * dim;
+            if (vec.vec16) {
+                for (int idx = tid; idx < nt * (DIM / 4); idx += WALK_THREADS) {
+                    const int i = (idx % (DIM / 4)) * 4, tt = idx / (DIM / 4);
+                    if (i < dim) copy_async16(dst + tt * TOK + a * DIM + i, src + (size_t)tt * vec.ld[a] + i);
+                }
+            } else {
+                for (int idx = tid; idx < nt * DIM; idx += WALK_THREADS) {
+                    const int i = idx % DIM, tt = idx / DIM;
+                    if (i < dim) copy_async4(dst + tt * TOK + a * DIM + i, src + (size_t)tt * vec.ld[a] + i);
+                }
+            }
+        }
+        for (int idx = tid; idx < nt * CPB; idx += WALK_THREADS) {
+            const int c_ = idx % CPB, tt = idx / CPB;
+            if (col0 + c_ < vd) copy_async4(dst + tt * TOK + NV * DIM + c_, v_in + (size_t)(t0 + tt) * ld_v + h * vd + col0 + c_);
+        }
+        if (DELTA && tid < nt) copy_async4(dst + tid * TOK + NV * DIM + CPB, beta + (size_t)(t0 + tid) * heads + h);
+    };
+#pragma unroll
+    for (int c = 0; c < WALK_STAGES - 1; ++c) {
+        if (c < n_chunks) issue(c);
+        copy_async_commit();
+    }
+    auto row_of = [&](int ii) { return ((ii >> 2) * RG + r) * 4 + (ii & 3); };
+    float S[ROWS];
+#pragma unroll
+    for (int ii = 0; ii < ROWS; ++ii) S[ii] = (live && row_of(ii) < dim) ? st[(size_t)row_of(ii) * vd + j] : 0.f;
+    for (int c = 0; c < n_chunks; ++c) {
+        copy_async_wait<WALK_STAGES - 2>();
+        __syncthreads();        // chunk c has arrived for every thread, and every thread has left chunk c - 1
+        if (c + WALK_STAGES - 1 < n_chunks) issue(c + WALK_STAGES - 1);
+        copy_async_commit();
+        const float* stage = buf[c % WALK_STAGES];
+        const int t0 = start + c * WALK_CHUNK, nt = min(WALK_CHUNK, end - t0);
+        for (int tt = 0; tt < nt; ++tt) {
+            const float* tok = stage + tt * TOK;
+            const float4* q4 = reinterpret_cast<const float4*>(tok);
+            const float v = tok[NV * DIM + cl];
+            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+            if constexpr (DELTA) {
+                const float4* k4 = reinterpret_cast<const float4*>(tok + DIM);
+                const float4* g4 = reinterpret_cast<const float4*>(tok + 2 * DIM);
+                const float bt = tok[NV * DIM + CPB];
+                float4 kk[ROWS / 4];
+                float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+                for (int g = 0; g < ROWS / 4; ++g) {
+                    const float4 k = k4[g * RG + r], gd = g4[g * RG + r];
+                    kk[g] = k;
+                    S[4 * g + 0] *= gd.x; a0 = fmaf(S[4 * g + 0], k.x, a0);
+                    S[4 * g + 1] *= gd.y; a1 = fmaf(S[4 * g + 1], k.y, a1);
+                    S[4 * g + 2] *= gd.z; a2 = fmaf(S[4 * g + 2], k.z, a2);
+                    S[4 * g + 3] *= gd.w; a3 = fmaf(S[4 * g + 3], k.w, a3);
+                }
+                const float u = bt * (v - sum_over_rows<RG>((a0 + a1) + (a2 + a3)));
+#pragma unroll
+                for (int g = 0; g < ROWS / 4; ++g) {
+                    const float4 q = q4[g * RG + r];
+                    S[4 * g + 0] = fmaf(kk[g].x, u, S[4 * g + 0]); o0 = fmaf(S[4 * g + 0], q.x, o0);
+                    S[4 * g + 1] = fmaf(kk[g].y, u, S[4 * g + 1]); o1 = fmaf(S[4 * g + 1], q.y, o1);
+                    S[4 * g + 2] = fmaf(kk[g].z, u, S[4 * g + 2]); o2 = fmaf(S[4 * g + 2], q.z, o2);
+                    S[4 * g + 3] = fmaf(kk[g].w, u, S[4 * g + 3]); o3 = fmaf(S[4 * g + 3], q.w, o3);
+                }
+            } else {
+                const float4* f4 = reinterpret_cast<const float4*>(tok + DIM);
+#pragma unroll
+                for (int g = 0; g < ROWS / 4; ++g) {
+                    const float4 q = q4[g * RG + r], f = f4[g * RG + r];
+                    S[4 * g + 0] = fmaf(f.x, S[4 * g + 0], (1.f - f.x) * v); o0 = fmaf(S[4 * g + 0], q.x, o0);
+                    S[4 * g + 1] = fmaf(f.y, S[4 * g + 1], (1.f - f.y) * v); o1 = fmaf(S[4 * g + 1], q.y, o1);
+                    S[4 * g + 2] = fmaf(f.z, S[4 * g + 2], (1.f - f.z) * v); o2 = fmaf(S[4 * g + 2], q.z, o2);
+                    S[4 * g + 3] = fmaf(f.w, S[4 * g + 3], (1.f - f.w) * v); o3 = fmaf(S[4 * g + 3], q.w, o3);
+                }
+            }
+            const float o = sum_over_rows<RG>((o0 + o1) + (o2 + o3));
+            if (live && r == 0) o_out[(size_t)(t0 + tt) * heads * vd + (size_t)h * vd + j] = o;
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int ii = 0; ii < ROWS; ++ii)
+            if (row_of(ii) < dim) st[(size_t)row_of(ii) * vd + j] = S[ii];
+    }
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 // ------------------------------------------------------------------------------------------------ conv state
 // New state of request b: the last taps - 1 rows of (old state ‖ the portion's projected values). One thread a
@@ -50,25 +213,40 @@ CELLM_API int cellm_conv_state_update(float* state, long long slot_stride, int n
 
 // ------------------------------------------------------------------------------------------------ HGRN2
 // proj row: q at col_q (heads x dim), forget gate at col_f (heads x dim), v at col_v (heads x vdim).
-// q = silu(.), f = lower + (1 - lower) sigmoid(. + f_bias). o_out [T, heads * vdim] gets S^T q (not normed).
-template <int DIM>
+// First, in place and for all tokens at once: q = silu(.), f = lower + (1 - lower) sigmoid(. + f_bias). Then the walk;
+// o_out [T, heads * vdim] gets S^T q (not normed).
+__global__ void __launch_bounds__(256)
+hgrn2_gates_kernel(float* __restrict__ proj, long long ld, int col_q, int col_f, const float* __restrict__ f_bias,
+                   const float* __restrict__ lower, int T, int n) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t total = (size_t)T * 2 * n;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const int c = (int)(idx % (2 * n));
+        float* row = proj + (idx / (2 * n)) * ld;
+        if (c < n) {
+            const float x = row[col_q + c];
+            row[col_q + c] = x * sigmoidf_(x);
+        } else {
+            const int i = c - n;
+            const float l = lower[i];
+            row[col_f + i] = l + (1.f - l) * sigmoidf_(row[col_f + i] + f_bias[i]);
+        }
+    }
+}
+
 __global__ void __launch_bounds__(32)
 hgrn2_scan_kernel(float* __restrict__ o_out, float* __restrict__ state, long long slot_stride, int n_slots,
                   const float* __restrict__ proj, long long ld, int col_q, int col_f, int col_v,
-                  const float* __restrict__ f_bias, const float* __restrict__ lower,
                   const int* __restrict__ cu_seqlens, const int* __restrict__ slot_ids, int heads, int dim, int vd,
                   int* __restrict__ err) {
     extern __shared__ float sm[];
     float* qs = sm;                 // [dim]
     float* fs = sm + dim;           // [dim]
-    float* Ssh = sm + 2 * dim;      // [dim][32] when the column does not live in registers
+    float* Ssh = sm + 2 * dim;      // [dim][32]: the warp's columns of S
     const int b = blockIdx.x, h = blockIdx.y, lane = threadIdx.x, j = blockIdx.z * 32 + lane;
-    float Sreg[DIM > 0 ? DIM : 1];
-    auto S = [&](int i) -> float& {
-        if constexpr (DIM > 0) return Sreg[i];
-        else return Ssh[i * 32 + lane];
-    };
-    const int n_rows = DIM > 0 ? DIM : dim;
+    auto S = [&](int i) -> float& { return Ssh[i * 32 + lane]; };
+    const int n_rows = dim;
     pdl_trigger();
     pdl_wait();
     const int slot = slot_ids[b];
@@ -81,10 +259,8 @@ hgrn2_scan_kernel(float* __restrict__ o_out, float* __restrict__ state, long lon
     for (int t = start; t < end; ++t) {
         const float* row = proj + (size_t)t * ld;
         for (int i = lane; i < dim; i += 32) {
-            const float xq = row[col_q + h * dim + i];
-            qs[i] = xq * sigmoidf_(xq);
-            const float l = lower[h * dim + i];
-            fs[i] = l + (1.f - l) * sigmoidf_(row[col_f + h * dim + i] + f_bias[h * dim + i]);
+            qs[i] = row[col_q + h * dim + i];
+            fs[i] = row[col_f + h * dim + i];
         }
         const float v = live ? row[col_v + h * vd + j] : 0.f;
         __syncwarp();
@@ -105,32 +281,41 @@ hgrn2_scan_kernel(float* __restrict__ o_out, float* __restrict__ state, long lon
     }
 }
 
+
 #define RECURRENT_MAX_DIM 512
 
-CELLM_API int cellm_hgrn2_scan(float* o_out, float* state, long long slot_stride, int n_slots, const float* proj, long long ld,
+CELLM_API int cellm_hgrn2_scan(float* o_out, float* state, long long slot_stride, int n_slots, float* proj, long long ld,
                                int col_q, int col_f, int col_v, const float* f_bias, const float* lower,
-                               const int* cu_seqlens, const int* slot_ids, int B, int heads, int dim, int vd, int* err,
+                               const int* cu_seqlens, const int* slot_ids, int B, int T, int heads, int dim, int vd, int* err,
                                cudaStream_t stream) {
-    if (B <= 0) return CELLM_OK;
+    if (B <= 0 || T <= 0) return CELLM_OK;
     if (heads <= 0 || dim <= 0 || vd <= 0 || dim > RECURRENT_MAX_DIM) return CELLM_ERR_SIZE;
-    const dim3 grid(B, heads, (vd + 31) / 32);
-#define HGRN2_RUN(D, smem)                                                                                         \
-    CELLM_RUN(hgrn2_scan_kernel<D>, grid, 32, smem, stream, o_out, state, slot_stride, n_slots, proj, ld, col_q, col_f, col_v, \
-              f_bias, lower, cu_seqlens, slot_ids, heads, dim, vd, err)
-    const size_t small = (size_t)2 * dim * sizeof(float);
-    if (dim == 16) HGRN2_RUN(16, small);
-    else if (dim == 32) HGRN2_RUN(32, small);
-    else if (dim == 64) HGRN2_RUN(64, small);
-    else if (dim == 128) HGRN2_RUN(128, small);
+    const size_t total = (size_t)T * 2 * heads * dim;
+    CELLM_RUN(hgrn2_gates_kernel, (unsigned)std::min<size_t>((total + 255) / 256, 148 * 16), 256, 0, stream, proj, ld, col_q, col_f, f_bias,
+              lower, T, heads * dim);
+    WalkVectors vec;
+    vec.p[0] = proj + col_q, vec.p[1] = proj + col_f, vec.p[2] = nullptr;
+    vec.ld[0] = vec.ld[1] = vec.ld[2] = ld;
+    vec.heads_per[0] = vec.heads_per[1] = vec.heads_per[2] = 1;
+    vec.vec16 = dim % 4 == 0 && ld % 4 == 0 && aligned16(vec.p[0]) && aligned16(vec.p[1]);
+#define HGRN2_WALK(D)                                                                                              \
+    CELLM_RUN((state_walk_kernel<D, false>), dim3(B, heads, (vd + WalkShape<D>::CPB - 1) / WalkShape<D>::CPB), WALK_THREADS, 0, stream, \
+              o_out, state, slot_stride, n_slots, vec, (const float*)(proj + col_v), ld, (const float*)nullptr, cu_seqlens, slot_ids,  \
+              heads, dim, vd, err)
+    if (dim <= 16) HGRN2_WALK(16);
+    else if (dim <= 32) HGRN2_WALK(32);
+    else if (dim <= 64) HGRN2_WALK(64);
+    else if (dim <= 128) HGRN2_WALK(128);
     else {
         const size_t big = (size_t)(2 + 32) * dim * sizeof(float);
         if (big > 48 * 1024) {
-            cudaError_t e = cudaFuncSetAttribute(hgrn2_scan_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)big);
+            cudaError_t e = cudaFuncSetAttribute(hgrn2_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)big);
             if (e != cudaSuccess) return (int)e;
         }
-        HGRN2_RUN(0, big);
+        CELLM_RUN(hgrn2_scan_kernel, dim3(B, heads, (vd + 31) / 32), 32, big, stream, o_out, state, slot_stride, n_slots,
+                  (const float*)proj, ld, col_q, col_f, col_v, cu_seqlens, slot_ids, heads, dim, vd, err);
     }
-#undef HGRN2_RUN
+#undef HGRN2_WALK
     return CELLM_OK;
 }
 
@@ -203,7 +388,6 @@ CELLM_API int cellm_delta_prep(float* qk, float* v_out, float* beta, float* deca
 
 // ------------------------------------------------------------------------------------------------ delta rule: the walk
 // qk [T, 2 * kvh * dim], v [T, heads * vd], beta [T, heads], decay [T, heads * dim] as delta_prep left them.
-template <int DIM>
 __global__ void __launch_bounds__(32)
 delta_scan_kernel(float* __restrict__ o_out, float* __restrict__ state, long long slot_stride, int n_slots,
                   const float* __restrict__ qk, const float* __restrict__ v_in, const float* __restrict__ beta,
@@ -213,15 +397,11 @@ delta_scan_kernel(float* __restrict__ o_out, float* __restrict__ state, long lon
     float* qs = sm;                 // [dim]
     float* ks = sm + dim;           // [dim]
     float* gs = sm + 2 * dim;       // [dim]
-    float* Ssh = sm + 3 * dim;      // [dim][32] when the column does not live in registers
+    float* Ssh = sm + 3 * dim;      // [dim][32]: the warp's columns of S
     const int b = blockIdx.x, h = blockIdx.y, lane = threadIdx.x, j = blockIdx.z * 32 + lane;
     const int g = h / (heads / kvh);
-    float Sreg[DIM > 0 ? DIM : 1];
-    auto S = [&](int i) -> float& {
-        if constexpr (DIM > 0) return Sreg[i];
-        else return Ssh[i * 32 + lane];
-    };
-    const int n_rows = DIM > 0 ? DIM : dim;
+    auto S = [&](int i) -> float& { return Ssh[i * 32 + lane]; };
+    const int n_rows = dim;
     pdl_trigger();
     pdl_wait();
     const int slot = slot_ids[b];
@@ -265,29 +445,35 @@ delta_scan_kernel(float* __restrict__ o_out, float* __restrict__ state, long lon
     }
 }
 
+
+
 CELLM_API int cellm_delta_scan(float* o_out, float* state, long long slot_stride, int n_slots, const float* qk, const float* v_in,
                                const float* beta, const float* decay, const int* cu_seqlens, const int* slot_ids, int B,
                                int heads, int kvh, int dim, int vd, int* err, cudaStream_t stream) {
     if (B <= 0) return CELLM_OK;
     if (heads <= 0 || kvh <= 0 || heads % kvh || dim <= 0 || vd <= 0 || dim > RECURRENT_MAX_DIM) return CELLM_ERR_SIZE;
-    const dim3 grid(B, heads, (vd + 31) / 32);
-#define DELTA_RUN(D, smem)                                                                                           \
-    CELLM_RUN(delta_scan_kernel<D>, grid, 32, smem, stream, o_out, state, slot_stride, n_slots, qk, v_in, beta, decay, cu_seqlens, \
-              slot_ids, heads, kvh, dim, vd, err)
-    const size_t small = (size_t)3 * dim * sizeof(float);
-    if (dim == 16) DELTA_RUN(16, small);
-    else if (dim == 32) DELTA_RUN(32, small);
-    else if (dim == 64) DELTA_RUN(64, small);
-    else if (dim == 128) DELTA_RUN(128, small);
+    WalkVectors vec;
+    vec.p[0] = qk, vec.p[1] = qk + (size_t)kvh * dim, vec.p[2] = decay;
+    vec.ld[0] = vec.ld[1] = 2LL * kvh * dim, vec.ld[2] = (long long)heads * dim;
+    vec.heads_per[0] = vec.heads_per[1] = heads / kvh, vec.heads_per[2] = 1;
+    vec.vec16 = dim % 4 == 0 && aligned16(qk) && aligned16(decay);
+#define DELTA_WALK(D)                                                                                              \
+    CELLM_RUN((state_walk_kernel<D, true>), dim3(B, heads, (vd + WalkShape<D>::CPB - 1) / WalkShape<D>::CPB), WALK_THREADS, 0, stream, \
+              o_out, state, slot_stride, n_slots, vec, v_in, (long long)heads * vd, beta, cu_seqlens, slot_ids, heads, dim, vd, err)
+    if (dim <= 16) DELTA_WALK(16);
+    else if (dim <= 32) DELTA_WALK(32);
+    else if (dim <= 64) DELTA_WALK(64);
+    else if (dim <= 128) DELTA_WALK(128);
     else {
         const size_t big = (size_t)(3 + 32) * dim * sizeof(float);
         if (big > 48 * 1024) {
-            cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)big);
+            cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)big);
             if (e != cudaSuccess) return (int)e;
         }
-        DELTA_RUN(0, big);
+        CELLM_RUN(delta_scan_kernel, dim3(B, heads, (vd + 31) / 32), 32, big, stream, o_out, state, slot_stride, n_slots, qk, v_in, beta,
+                  decay, cu_seqlens, slot_ids, heads, kvh, dim, vd, err);
     }
-#undef DELTA_RUN
+#undef DELTA_WALK
     return CELLM_OK;
 }
 

@@ -38,3 +38,25 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None)
         rec.params.w.tc_ok = 0
     part_program(a.dtype, a.device, a.shape[1]).run_part(rec, a, None, out=c, rows=a.shape[0])
     return c
+
+
+ACTIVATION_CODES = {"gelu": 0, "gelu_tanh": 1, "silu": 2, "relu": 3, "relu2": 4}
+
+
+def gemm_act(a: torch.Tensor, w: torch.Tensor, act: str, out_dtype: torch.dtype) -> torch.Tensor:
+    """act(a [M, K] . w [N, K]^T) with the activation formed on the 32-bit sums. bfloat16 operands of more than 16 rows:
+    the persistent tensor-core product with the activation in its epilogue; otherwise the product with 32-bit output
+    and the activation as a kernel of its own."""
+    M, K = a.shape
+    if (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and M > 16 and K % 8 == 0 and a.stride(1) == 1 and w.stride(1) == 1
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and out_dtype in (torch.bfloat16, torch.float32)):
+        from ._state import error_word
+        N = w.shape[0]
+        c = torch.empty((M, N), dtype=out_dtype, device=a.device)
+        check(fn("gemm_tcgen05", "cellm_gemm_grouped_tcgen05")(ptr(c), ptr(a), ptr(w), M, N, K, 1, a.stride(0), w.stride(0), N, tag(out_dtype),
+                                                              None, ACTIVATION_CODES[act], ptr(error_word(a.device)), stream_of(a)),
+              "gemm_grouped_tcgen05")
+        return c
+    from .recurrent import activation
+    return activation(gemm(a, w, torch.float32), act, out_dtype)

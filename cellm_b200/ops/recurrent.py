@@ -146,11 +146,12 @@ def attention_flash_sink(q: torch.Tensor, cache, ctx, nh: int, nkv: int, hd: int
 def hgrn2_scan(proj: torch.Tensor, col_q: int, col_f: int, col_v: int, f_bias: torch.Tensor, lower: torch.Tensor, state: torch.Tensor,
                ctx, heads: int, dim: int, vd: int) -> torch.Tensor:
     """The HGRN2 recurrence over every request's tokens of the step; state [slots, heads, dim, vd] float32 is moved on.
-    Returns S^T q per token and head, float32 [T, heads * vd]."""
+    Returns S^T q per token and head, float32 [T, heads * vd]. The q and f columns of `proj` are replaced by silu(q) and
+    by the forget gate."""
     _f32(proj, f_bias, lower, state)
     o = torch.empty((ctx.T, heads * vd), dtype=torch.float32, device=proj.device)
     check(fn(_LIB, "cellm_hgrn2_scan")(ptr(o), ptr(state), state.stride(0), state.shape[0], ptr(proj), proj.stride(0), int(col_q), int(col_f),
-                                       int(col_v), ptr(f_bias), ptr(lower), ptr(ctx.cu_seqlens), ptr(ctx.slot_ids), ctx.B, heads, dim, vd,
+                                       int(col_v), ptr(f_bias), ptr(lower), ptr(ctx.cu_seqlens), ptr(ctx.slot_ids), ctx.B, ctx.T, heads, dim, vd,
                                        ptr(ctx.err), stream_of(proj)), "hgrn2_scan")
     return o
 

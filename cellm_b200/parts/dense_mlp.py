@@ -1,5 +1,6 @@
 """Plain two-matrix feed-forward: W_down act(W_up h), with act one of "relu2" (the square of relu), "relu", "silu",
-"gelu", "gelu_tanh". The first product keeps its 32-bit sums until the activation is formed."""
+"gelu", "gelu_tanh". The activation is formed on the first product's 32-bit sums: in that product's epilogue for prompt
+portions under bfloat16, by a kernel of its own otherwise."""
 from __future__ import annotations
 
 import torch
@@ -31,8 +32,9 @@ class DenseMLP(FeedForward):
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         from .. import ops
-        u = self.up(x, out_dtype=torch.float32)
-        return self.down(ops.activation(u, self.activation, self.dtype))
+        if self.up.weight.dtype != x.dtype:          # a matrix kept in 32-bit under bfloat16 activations
+            return self.down(ops.activation(self.up(x, out_dtype=torch.float32), self.activation, self.dtype))
+        return self.down(ops.gemm_act(x, self.up.weight, self.activation, self.dtype))
 
 
 register_feed_forward("dense_mlp", DenseMLP)

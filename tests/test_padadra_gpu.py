@@ -352,7 +352,7 @@ def cuts_of(T, sizes):
     return out
 
 
-@pytest.mark.parametrize("heads,dim,vd", [(2, 16, 24), (1, 32, 32), (3, 5, 6), (1, 128, 40), (2, 48, 70), (1, 64, 128)])
+@pytest.mark.parametrize("heads,dim,vd", [(2, 16, 24), (1, 32, 32), (3, 5, 6), (1, 128, 40), (2, 48, 70), (1, 64, 128), (2, 17, 3), (1, 160, 20)])
 def test_hgrn2_recurrence_alone(heads, dim, vd):
     """Two sequences side by side in slots 3 and 1, fed whole and in portions down to one token: the walk against the
     plain recurrence in 64-bit, and the cuttings against each other bit for bit."""
@@ -397,7 +397,7 @@ def test_hgrn2_recurrence_alone(heads, dim, vd):
         assert torch.equal(outs["whole"][b], outs["portions"][b]) and torch.equal(outs["whole"][b], outs["single"][b])
 
 
-@pytest.mark.parametrize("heads,kvh,dim,vd", [(4, 2, 16, 8), (2, 2, 64, 64), (3, 1, 6, 10), (2, 1, 48, 33), (1, 1, 128, 32)])
+@pytest.mark.parametrize("heads,kvh,dim,vd", [(4, 2, 16, 8), (2, 2, 64, 64), (3, 1, 6, 10), (2, 1, 48, 33), (1, 1, 128, 32), (2, 1, 33, 5), (1, 1, 136, 12)])
 def test_delta_rule_alone(heads, kvh, dim, vd):
     """The walk of the gated delta rule given its inputs (unit q and k, values, beta, decays), against 64-bit."""
     from cellm_b200 import ops
@@ -510,6 +510,19 @@ def test_stream_kernels_and_activation():
     torch.testing.assert_close(xs.cpu().double(), x.double() + 0.3 * (a.double() + b.double()), rtol=1e-6, atol=1e-6)
     u = ops.activation(a.to(DEV), "relu2", torch.float32)
     torch.testing.assert_close(u.cpu().double(), torch.relu(a.double()) ** 2, rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("M,K,N", [(300, 64, 200), (17, 128, 96), (8, 64, 80), (2048, 256, 1000)])
+def test_product_with_the_activation_in_its_epilogue(M, K, N):
+    """Prompt portions under bfloat16 form the feed-forward's activation on the 32-bit sums in the product itself."""
+    from cellm_b200 import ops
+    g = torch.Generator().manual_seed(M)
+    a, w = torch.randn(M, K, generator=g).bfloat16(), (torch.randn(N, K, generator=g) * 0.2).bfloat16()
+    want = torch.relu(a.double() @ w.double().T) ** 2
+    got = ops.gemm_act(a.to(DEV), w.to(DEV), "relu2", torch.bfloat16).cpu().double()
+    torch.testing.assert_close(got, want, rtol=2 ** -7, atol=1e-3)
+    got32 = ops.gemm_act(a.to(DEV).float(), w.to(DEV).float(), "relu2", torch.float32).cpu().double()
+    torch.testing.assert_close(got32, want, rtol=1e-5, atol=1e-5)
 
 
 @pytest.mark.parametrize("hd,window", [(64, 50), (32, 0), (128, 7)])
