@@ -8,30 +8,35 @@
 // from the state the step before left. The walk and the order of every sum depend on the head's sizes alone, not on
 // how the sequence was cut, so the state after a token is bit-identical. Everything that enters the recurrence is
 // 32-bit: the projections come as 32-bit sums. Heads of more than 128 rows keep a warp's 32 columns in shared memory
-// (`*_scan_kernel`); the others live in registers (`*_walk_kernel`).
+// (`*_scan_kernel`); the others live in registers (`state_walk_kernel`).
 //
 // Also here: the update of a short convolution's state (conv_taps.cuh), the preparation of the delta rule's
 // inputs (convolution + silu, unit vectors, beta, decays), and the norm over a head's output with an optional gate.
+#include <algorithm>
+
 #include "conv_taps.cuh"
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
 
 // ------------------------------------------------------------------------------------------------ the walk
-// Heads of up to 128 rows: a column of S is shared by RG neighbouring lanes, each holding DIM / RG of its rows in
-// registers (rows in groups of four, dealt round robin to the lanes, so that a lane's 16-byte reads of the token's
-// vectors in shared memory fall into different banks), and a block of four warps walks 128 / RG neighbouring columns
-// of one (request, head). The tokens' vectors over the rows, the block's entries of v and beta come in chunks of
-// eight tokens through asynchronous copies into three stages of shared memory, two chunks ahead of the one in use:
-// a chunk costs one barrier and no wait for memory, and within a chunk the warps run free. Sums over a column's rows
-// are added lane by lane (shuffles) in a fixed order. DIM is the next of 16, 32, 64, 128 above the head's rows; the
-// rows beyond are zeros that nothing reads back.
-template <int DIM> struct WalkShape {
-    static constexpr int RG = DIM >= 64 ? 8 : (DIM == 32 ? 4 : 2);
-    static constexpr int ROWS = DIM / RG;          // rows of a column in one lane: 16 or 8
+// Heads of up to 128 rows. The walk is a chain of dependent steps, token after token, and a head's state is small: one
+// request's walk is bound by the chain's latency, many requests' walks by the instructions issued. A column of S is
+// shared by DIM / ROWS neighbouring lanes, each holding ROWS of its rows in registers (eight for heads of 64 and 128
+// rows, four below: measured, more lanes a column cost more in the sums over the lanes than their warps hide), in
+// groups of four dealt round robin to the lanes, so that the lanes' 16-byte reads of the token's vectors in shared
+// memory are neighbours. A block of eight warps walks 256 / (DIM / ROWS) neighbouring columns of one (request, head).
+// The tokens' vectors over the rows, the block's entries of v and beta come in chunks of eight tokens through
+// asynchronous copies into three stages of shared memory, two chunks ahead of the one in use: a chunk costs one
+// barrier and no wait for memory, and within a chunk the warps run free, a whole chunk unrolled so that a token's
+// loads and the sums of the token before overlap. Sums over a column's rows are added lane by lane (shuffles) in a
+// fixed order. The block's tile of S goes through shared memory on its way in and out, in rows of whole sectors.
+// DIM is the next of 16, 32, 64, 128 above the head's rows; the rows beyond are zeros that nothing reads back.
+template <int DIM, int ROWS> struct WalkShape {
+    static constexpr int RG = DIM / ROWS;          // lanes a column
     static constexpr int CPW = 32 / RG;            // columns a warp
-    static constexpr int CPB = 4 * CPW;            // columns a block
+    static constexpr int CPB = 8 * CPW;            // columns a block
 };
-#define WALK_THREADS 128
+#define WALK_THREADS 256
 #define WALK_CHUNK 8
 #define WALK_STAGES 3
 
@@ -59,16 +64,17 @@ struct WalkVectors {
     int vec16;          // every start is a multiple of 16 bytes: copies of four values
 };
 
-template <int DIM, bool DELTA>
+template <int DIM, int ROWS, bool DELTA>
 __global__ void __launch_bounds__(WALK_THREADS)
 state_walk_kernel(float* __restrict__ o_out, float* __restrict__ state, long long slot_stride, int n_slots, const WalkVectors vec,
                   const float* __restrict__ v_in, long long ld_v, const float* __restrict__ beta,
                   const int* __restrict__ cu_seqlens, const int* __restrict__ slot_ids, int heads, int dim, int vd,
                   int* __restrict__ err) {
-    using W = WalkShape<DIM>;
-    constexpr int RG = W::RG, ROWS = W::ROWS, CPB = W::CPB, NV = DELTA ? 3 : 2;
+    using W = WalkShape<DIM, ROWS>;
+    constexpr int RG = W::RG, CPB = W::CPB, NV = DELTA ? 3 : 2, NG = ROWS / 4;
     constexpr int TOK = NV * DIM + CPB + 4;          // a token in a stage: its vectors | the block's entries of v | beta
     __shared__ __align__(16) float buf[WALK_STAGES][WALK_CHUNK * TOK];
+    __shared__ float tile[DIM][CPB + 1];             // the block's columns of S on their way in and out
     const int b = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int r = lane % RG, cl = warp * W::CPW + lane / RG, col0 = blockIdx.z * CPB, j = col0 + cl;
     pdl_trigger();
@@ -113,10 +119,57 @@ state_walk_kernel(float* __restrict__ o_out, float* __restrict__ state, long lon
         if (c < n_chunks) issue(c);
         copy_async_commit();
     }
-    auto row_of = [&](int ii) { return ((ii >> 2) * RG + r) * 4 + (ii & 3); };
+    for (int idx = tid; idx < DIM * CPB; idx += WALK_THREADS) {
+        const int row = idx / CPB, c_ = idx % CPB;
+        tile[row][c_] = (row < dim && col0 + c_ < vd) ? st[(size_t)row * vd + col0 + c_] : 0.f;
+    }
+    __syncthreads();
+    // the lane's rows: groups of four, group g at rows (g * RG + r) * 4 ..
     float S[ROWS];
 #pragma unroll
-    for (int ii = 0; ii < ROWS; ++ii) S[ii] = (live && row_of(ii) < dim) ? st[(size_t)row_of(ii) * vd + j] : 0.f;
+    for (int ii = 0; ii < ROWS; ++ii) S[ii] = tile[((ii >> 2) * RG + r) * 4 + (ii & 3)][cl];
+    // one token: the lane's rows of the column move on, and lane r == 0 of the column writes its read-out
+    auto token = [&](const float* tok, int t) {
+        const float4* q4 = reinterpret_cast<const float4*>(tok);
+        const float v = tok[NV * DIM + cl];
+        float o0 = 0.f, o1 = 0.f;
+        if constexpr (DELTA) {
+            const float4* k4 = reinterpret_cast<const float4*>(tok + DIM);
+            const float4* g4 = reinterpret_cast<const float4*>(tok + 2 * DIM);
+            const float bt = tok[NV * DIM + CPB];
+            float4 kk[NG];
+            float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+            for (int g = 0; g < NG; ++g) {
+                const float4 k = k4[g * RG + r], gd = g4[g * RG + r];
+                kk[g] = k;
+                S[4 * g + 0] *= gd.x, S[4 * g + 1] *= gd.y, S[4 * g + 2] *= gd.z, S[4 * g + 3] *= gd.w;
+                a0 = fmaf(S[4 * g + 0], k.x, a0), a1 = fmaf(S[4 * g + 1], k.y, a1);
+                a0 = fmaf(S[4 * g + 2], k.z, a0), a1 = fmaf(S[4 * g + 3], k.w, a1);
+            }
+            const float u = bt * (v - sum_over_rows<RG>(a0 + a1));
+#pragma unroll
+            for (int g = 0; g < NG; ++g) {
+                const float4 q = q4[g * RG + r];
+                S[4 * g + 0] = fmaf(kk[g].x, u, S[4 * g + 0]), S[4 * g + 1] = fmaf(kk[g].y, u, S[4 * g + 1]);
+                S[4 * g + 2] = fmaf(kk[g].z, u, S[4 * g + 2]), S[4 * g + 3] = fmaf(kk[g].w, u, S[4 * g + 3]);
+                o0 = fmaf(S[4 * g + 0], q.x, o0), o1 = fmaf(S[4 * g + 1], q.y, o1);
+                o0 = fmaf(S[4 * g + 2], q.z, o0), o1 = fmaf(S[4 * g + 3], q.w, o1);
+            }
+        } else {
+            const float4* f4 = reinterpret_cast<const float4*>(tok + DIM);
+#pragma unroll
+            for (int g = 0; g < NG; ++g) {
+                const float4 q = q4[g * RG + r], f = f4[g * RG + r];
+                S[4 * g + 0] = fmaf(f.x, S[4 * g + 0], (1.f - f.x) * v), S[4 * g + 1] = fmaf(f.y, S[4 * g + 1], (1.f - f.y) * v);
+                S[4 * g + 2] = fmaf(f.z, S[4 * g + 2], (1.f - f.z) * v), S[4 * g + 3] = fmaf(f.w, S[4 * g + 3], (1.f - f.w) * v);
+                o0 = fmaf(S[4 * g + 0], q.x, o0), o1 = fmaf(S[4 * g + 1], q.y, o1);
+                o0 = fmaf(S[4 * g + 2], q.z, o0), o1 = fmaf(S[4 * g + 3], q.w, o1);
+            }
+        }
+        const float o = sum_over_rows<RG>(o0 + o1);
+        if (live && r == 0) o_out[(size_t)t * heads * vd + (size_t)h * vd + j] = o;
+    };
     for (int c = 0; c < n_chunks; ++c) {
         copy_async_wait<WALK_STAGES - 2>();
         __syncthreads();        // chunk c has arrived for every thread, and every thread has left chunk c - 1
@@ -124,54 +177,20 @@ state_walk_kernel(float* __restrict__ o_out, float* __restrict__ state, long lon
         copy_async_commit();
         const float* stage = buf[c % WALK_STAGES];
         const int t0 = start + c * WALK_CHUNK, nt = min(WALK_CHUNK, end - t0);
-        for (int tt = 0; tt < nt; ++tt) {
-            const float* tok = stage + tt * TOK;
-            const float4* q4 = reinterpret_cast<const float4*>(tok);
-            const float v = tok[NV * DIM + cl];
-            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
-            if constexpr (DELTA) {
-                const float4* k4 = reinterpret_cast<const float4*>(tok + DIM);
-                const float4* g4 = reinterpret_cast<const float4*>(tok + 2 * DIM);
-                const float bt = tok[NV * DIM + CPB];
-                float4 kk[ROWS / 4];
-                float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        if (nt == WALK_CHUNK) {
 #pragma unroll
-                for (int g = 0; g < ROWS / 4; ++g) {
-                    const float4 k = k4[g * RG + r], gd = g4[g * RG + r];
-                    kk[g] = k;
-                    S[4 * g + 0] *= gd.x; a0 = fmaf(S[4 * g + 0], k.x, a0);
-                    S[4 * g + 1] *= gd.y; a1 = fmaf(S[4 * g + 1], k.y, a1);
-                    S[4 * g + 2] *= gd.z; a2 = fmaf(S[4 * g + 2], k.z, a2);
-                    S[4 * g + 3] *= gd.w; a3 = fmaf(S[4 * g + 3], k.w, a3);
-                }
-                const float u = bt * (v - sum_over_rows<RG>((a0 + a1) + (a2 + a3)));
-#pragma unroll
-                for (int g = 0; g < ROWS / 4; ++g) {
-                    const float4 q = q4[g * RG + r];
-                    S[4 * g + 0] = fmaf(kk[g].x, u, S[4 * g + 0]); o0 = fmaf(S[4 * g + 0], q.x, o0);
-                    S[4 * g + 1] = fmaf(kk[g].y, u, S[4 * g + 1]); o1 = fmaf(S[4 * g + 1], q.y, o1);
-                    S[4 * g + 2] = fmaf(kk[g].z, u, S[4 * g + 2]); o2 = fmaf(S[4 * g + 2], q.z, o2);
-                    S[4 * g + 3] = fmaf(kk[g].w, u, S[4 * g + 3]); o3 = fmaf(S[4 * g + 3], q.w, o3);
-                }
-            } else {
-                const float4* f4 = reinterpret_cast<const float4*>(tok + DIM);
-#pragma unroll
-                for (int g = 0; g < ROWS / 4; ++g) {
-                    const float4 q = q4[g * RG + r], f = f4[g * RG + r];
-                    S[4 * g + 0] = fmaf(f.x, S[4 * g + 0], (1.f - f.x) * v); o0 = fmaf(S[4 * g + 0], q.x, o0);
-                    S[4 * g + 1] = fmaf(f.y, S[4 * g + 1], (1.f - f.y) * v); o1 = fmaf(S[4 * g + 1], q.y, o1);
-                    S[4 * g + 2] = fmaf(f.z, S[4 * g + 2], (1.f - f.z) * v); o2 = fmaf(S[4 * g + 2], q.z, o2);
-                    S[4 * g + 3] = fmaf(f.w, S[4 * g + 3], (1.f - f.w) * v); o3 = fmaf(S[4 * g + 3], q.w, o3);
-                }
-            }
-            const float o = sum_over_rows<RG>((o0 + o1) + (o2 + o3));
-            if (live && r == 0) o_out[(size_t)(t0 + tt) * heads * vd + (size_t)h * vd + j] = o;
+            for (int tt = 0; tt < WALK_CHUNK; ++tt) token(stage + tt * TOK, t0 + tt);
+        } else {
+            for (int tt = 0; tt < nt; ++tt) token(stage + tt * TOK, t0 + tt);
         }
     }
-    if (live) {
+    __syncthreads();
 #pragma unroll
-        for (int ii = 0; ii < ROWS; ++ii)
-            if (row_of(ii) < dim) st[(size_t)row_of(ii) * vd + j] = S[ii];
+    for (int ii = 0; ii < ROWS; ++ii) tile[((ii >> 2) * RG + r) * 4 + (ii & 3)][cl] = S[ii];
+    __syncthreads();
+    for (int idx = tid; idx < DIM * CPB; idx += WALK_THREADS) {
+        const int row = idx / CPB, c_ = idx % CPB;
+        if (row < dim && col0 + c_ < vd) st[(size_t)row * vd + col0 + c_] = tile[row][c_];
     }
 }
 
@@ -298,14 +317,14 @@ CELLM_API int cellm_hgrn2_scan(float* o_out, float* state, long long slot_stride
     vec.ld[0] = vec.ld[1] = vec.ld[2] = ld;
     vec.heads_per[0] = vec.heads_per[1] = vec.heads_per[2] = 1;
     vec.vec16 = dim % 4 == 0 && ld % 4 == 0 && aligned16(vec.p[0]) && aligned16(vec.p[1]);
-#define HGRN2_WALK(D)                                                                                              \
-    CELLM_RUN((state_walk_kernel<D, false>), dim3(B, heads, (vd + WalkShape<D>::CPB - 1) / WalkShape<D>::CPB), WALK_THREADS, 0, stream, \
+#define HGRN2_WALK(D, R)                                                                                           \
+    CELLM_RUN((state_walk_kernel<D, R, false>), dim3(B, heads, (vd + WalkShape<D, R>::CPB - 1) / WalkShape<D, R>::CPB), WALK_THREADS, 0, stream, \
               o_out, state, slot_stride, n_slots, vec, (const float*)(proj + col_v), ld, (const float*)nullptr, cu_seqlens, slot_ids,  \
               heads, dim, vd, err)
-    if (dim <= 16) HGRN2_WALK(16);
-    else if (dim <= 32) HGRN2_WALK(32);
-    else if (dim <= 64) HGRN2_WALK(64);
-    else if (dim <= 128) HGRN2_WALK(128);
+    if (dim <= 16) HGRN2_WALK(16, 4);
+    else if (dim <= 32) HGRN2_WALK(32, 4);
+    else if (dim <= 64) HGRN2_WALK(64, 8);
+    else if (dim <= 128) HGRN2_WALK(128, 8);
     else {
         const size_t big = (size_t)(2 + 32) * dim * sizeof(float);
         if (big > 48 * 1024) {
@@ -320,7 +339,7 @@ CELLM_API int cellm_hgrn2_scan(float* o_out, float* state, long long slot_stride
 }
 
 // ------------------------------------------------------------------------------------------------ delta rule: inputs
-// One block a token. proj row: q (kvh x dim), k (kvh x dim), v (heads x vdim) from col0 on, side by side (the
+// A few blocks a token. proj row: q (kvh x dim), k (kvh x dim), v (heads x vdim) from col0 on, side by side (the
 // convolution's channels in this order), beta's pre-activation at col_b (heads). a2 [T, heads * dim]: the decay's
 // pre-activation without its bias. Writes qk [T, 2 * kvh * dim] (unit q times dim^-1/2, then unit k), v [T, heads * vdim],
 // beta [T, heads], decay [T, heads * dim] = exp(-exp(A_log_h) * softplus(a2 + dt_bias)).
@@ -330,36 +349,42 @@ delta_prep_kernel(float* __restrict__ qk, float* __restrict__ v_out, float* __re
                   const float* __restrict__ a2, const float* __restrict__ dt_bias, const float* __restrict__ A_log,
                   const int* __restrict__ seq_of_token, const int* __restrict__ cu_seqlens, const int* __restrict__ slot_ids,
                   int heads, int kvh, int dim, int vd, float l2_eps, int* __restrict__ err) {
-    extern __shared__ float buf[];      // [2 * kvh * dim + heads * vd]
+    extern __shared__ float buf[];      // [warps][dim]: a q or k head of the token
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x, b = seq_of_token[t], start = cu_seqlens[b];
     int slot = slot_ids[b];
-    if (slot < 0 || slot >= n_slots) { if (threadIdx.x == 0) atomicOr(err, CELLM_DEV_BAD_SLOT); slot = 0; }
+    if (slot < 0 || slot >= n_slots) { if (threadIdx.x == 0 && blockIdx.y == 0) atomicOr(err, CELLM_DEV_BAD_SLOT); slot = 0; }
     cv.state = state_base + (size_t)slot * slot_stride;
-    const int Cqk = 2 * kvh * dim, C = cv.C;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
-        const float y = conv_taps_at(cv, t, start, c);
-        buf[c] = y * sigmoidf_(y);
-    }
-    __syncthreads();
+    const int Cqk = 2 * kvh * dim;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const int part = blockIdx.y, parts = gridDim.y, thread = part * blockDim.x + threadIdx.x, threads = parts * blockDim.x;
+    // q and k: a warp a head (convolution + silu, then the unit vector); the token's parts share the heads
     const float q_scale = rsqrtf((float)dim);
-    for (int hh = warp; hh < 2 * kvh; hh += nwarps) {
-        const float* x = buf + hh * dim;
+    float* x = buf + warp * dim;
+    for (int hh = part * nwarps + warp; hh < 2 * kvh; hh += parts * nwarps) {
         float ss = 0.f;
-        for (int i = lane; i < dim; i += 32) ss = fmaf(x[i], x[i], ss);
+        for (int i = lane; i < dim; i += 32) {
+            const float y = conv_taps_at(cv, t, start, hh * dim + i);
+            const float a = y * sigmoidf_(y);
+            x[i] = a;
+            ss = fmaf(a, a, ss);
+        }
         ss = warp_sum(ss);
         const float r = (1.f / sqrtf(ss + l2_eps)) * (hh < kvh ? q_scale : 1.f);
-        for (int i = lane; i < dim; i += 32) qk[(size_t)t * Cqk + hh * dim + i] = x[i] * r;
+        for (int i = lane; i < dim; i += 32) qk[(size_t)t * Cqk + hh * dim + i] = x[i] * r;     // a lane reads back its own entries
     }
     const int Cv = heads * vd;
-    for (int c = threadIdx.x; c < Cv; c += blockDim.x) v_out[(size_t)t * Cv + c] = buf[Cqk + c];
-    for (int h = threadIdx.x; h < heads; h += blockDim.x)
-        beta[(size_t)t * heads + h] = sigmoidf_(cv.proj[(size_t)t * cv.ld + col_b + h]);
-    for (int idx = threadIdx.x; idx < heads * dim; idx += blockDim.x) {
-        const float x = a2[(size_t)t * heads * dim + idx] + dt_bias[idx];
-        const float sp = x > 20.f ? x : log1pf(expf(x));
+    for (int c = thread; c < Cv; c += threads) {
+        const float y = conv_taps_at(cv, t, start, Cqk + c);
+        v_out[(size_t)t * Cv + c] = y * sigmoidf_(y);
+    }
+    if (part == 0)
+        for (int h = threadIdx.x; h < heads; h += blockDim.x)
+            beta[(size_t)t * heads + h] = sigmoidf_(cv.proj[(size_t)t * cv.ld + col_b + h]);
+    for (int idx = thread; idx < heads * dim; idx += threads) {
+        const float xa = a2[(size_t)t * heads * dim + idx] + dt_bias[idx];
+        const float sp = xa > 20.f ? xa : log1pf(expf(xa));
         decay[(size_t)t * heads * dim + idx] = expf(-expf(A_log[idx / dim]) * sp);
     }
 }
@@ -375,14 +400,11 @@ CELLM_API int cellm_delta_prep(float* qk, float* v_out, float* beta, float* deca
     ConvTaps cv;
     cv.proj = proj; cv.ld = ld; cv.col0 = col0; cv.bias = nullptr; cv.taps = taps; cv.state = nullptr; cv.n_taps = n_taps;
     cv.C = 2 * kvh * dim + heads * vd;
-    const size_t smem = (size_t)cv.C * sizeof(float);
-    if (smem > 200 * 1024) return CELLM_ERR_SIZE;
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(delta_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-    }
-    CELLM_RUN(delta_prep_kernel, T, 256, smem, stream, qk, v_out, beta, decay, cv, slot_stride, n_slots, state, col_b, a2, dt_bias,
-              A_log, seq_of_token, cu_seqlens, slot_ids, heads, kvh, dim, vd, l2_eps, err);
+    if (dim > RECURRENT_MAX_DIM) return CELLM_ERR_SIZE;
+    // a token's channels over as many blocks as leave a thread about four of them
+    const int widest = std::max(cv.C, heads * dim), parts = std::max(1, std::min((widest + 1023) / 1024, 64));
+    CELLM_RUN(delta_prep_kernel, dim3(T, parts), 256, (size_t)8 * dim * sizeof(float), stream, qk, v_out, beta, decay, cv, slot_stride,
+              n_slots, state, col_b, a2, dt_bias, A_log, seq_of_token, cu_seqlens, slot_ids, heads, kvh, dim, vd, l2_eps, err);
     return CELLM_OK;
 }
 
@@ -457,13 +479,13 @@ CELLM_API int cellm_delta_scan(float* o_out, float* state, long long slot_stride
     vec.ld[0] = vec.ld[1] = 2LL * kvh * dim, vec.ld[2] = (long long)heads * dim;
     vec.heads_per[0] = vec.heads_per[1] = heads / kvh, vec.heads_per[2] = 1;
     vec.vec16 = dim % 4 == 0 && aligned16(qk) && aligned16(decay);
-#define DELTA_WALK(D)                                                                                              \
-    CELLM_RUN((state_walk_kernel<D, true>), dim3(B, heads, (vd + WalkShape<D>::CPB - 1) / WalkShape<D>::CPB), WALK_THREADS, 0, stream, \
+#define DELTA_WALK(D, R)                                                                                           \
+    CELLM_RUN((state_walk_kernel<D, R, true>), dim3(B, heads, (vd + WalkShape<D, R>::CPB - 1) / WalkShape<D, R>::CPB), WALK_THREADS, 0, stream, \
               o_out, state, slot_stride, n_slots, vec, v_in, (long long)heads * vd, beta, cu_seqlens, slot_ids, heads, dim, vd, err)
-    if (dim <= 16) DELTA_WALK(16);
-    else if (dim <= 32) DELTA_WALK(32);
-    else if (dim <= 64) DELTA_WALK(64);
-    else if (dim <= 128) DELTA_WALK(128);
+    if (dim <= 16) DELTA_WALK(16, 4);
+    else if (dim <= 32) DELTA_WALK(32, 4);
+    else if (dim <= 64) DELTA_WALK(64, 8);
+    else if (dim <= 128) DELTA_WALK(128, 8);
     else {
         const size_t big = (size_t)(3 + 32) * dim * sizeof(float);
         if (big > 48 * 1024) {

@@ -12,7 +12,7 @@
 #include "conv_taps.cuh"
 
 template <typename TA>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 sink_attn_prep_kernel(TA* __restrict__ q_out, TA* __restrict__ k_pool, TA* __restrict__ v_pool, ConvTaps cv,
                       const float* __restrict__ state_base, long long slot_stride, int n_slots,
                       const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
@@ -112,13 +112,15 @@ CELLM_API int cellm_sink_attn_prep(void* q_out, void* k_pool, void* v_pool, cons
     cv.C = nh * hd + nkv * hd + nkv * vd;
     const size_t smem = (size_t)(cv.C + rot + vd) * sizeof(float);
     if (smem > 200 * 1024) return CELLM_ERR_SIZE;
+    // a thread about four channels: the convolution's loads of one channel wait on nothing of another's
+    const int threads = cv.C >= 4096 ? 1024 : cv.C >= 2048 ? 512 : 256;
 #define PREP_RUN(TA)                                                                                                          \
     do {                                                                                                                      \
         if (smem > 48 * 1024) {                                                                                               \
             cudaError_t e = cudaFuncSetAttribute(sink_attn_prep_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) return (int)e;                                                                              \
         }                                                                                                                     \
-        CELLM_RUN(sink_attn_prep_kernel<TA>, T, 256, smem, stream, (TA*)q_out, (TA*)k_pool, (TA*)v_pool, cv, state, slot_stride, \
+        CELLM_RUN(sink_attn_prep_kernel<TA>, T, threads, smem, stream, (TA*)q_out, (TA*)k_pool, (TA*)v_pool, cv, state, slot_stride, \
                   n_slots, q_norm_w, k_norm_w, eps, qk_freq, rot, v_freq, interleaved, positions, seq_of_token, cu_seqlens, \
                   slot_ids, block_table, bt_stride, num_pages, page_size, nh, nkv, hd, vd, err);                             \
     } while (0)
