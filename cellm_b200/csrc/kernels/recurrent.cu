@@ -401,8 +401,8 @@ CELLM_API int cellm_delta_prep(float* qk, float* v_out, float* beta, float* deca
     cv.proj = proj; cv.ld = ld; cv.col0 = col0; cv.bias = nullptr; cv.taps = taps; cv.state = nullptr; cv.n_taps = n_taps;
     cv.C = 2 * kvh * dim + heads * vd;
     if (dim > RECURRENT_MAX_DIM) return CELLM_ERR_SIZE;
-    // a token's channels over as many blocks as leave a thread about four of them
-    const int widest = std::max(cv.C, heads * dim), parts = std::max(1, std::min((widest + 1023) / 1024, 64));
+    // few tokens: a token's channels over as many blocks as leave a thread about four of them (no sum crosses blocks)
+    const int widest = std::max(cv.C, heads * dim), parts = T >= 512 ? 1 : std::max(1, std::min((widest + 1023) / 1024, 64));
     CELLM_RUN(delta_prep_kernel, dim3(T, parts), 256, (size_t)8 * dim * sizeof(float), stream, qk, v_out, beta, decay, cv, slot_stride,
               n_slots, state, col_b, a2, dt_bias, A_log, seq_of_token, cu_seqlens, slot_ids, heads, kvh, dim, vd, l2_eps, err);
     return CELLM_OK;

@@ -112,8 +112,9 @@ CELLM_API int cellm_sink_attn_prep(void* q_out, void* k_pool, void* v_pool, cons
     cv.C = nh * hd + nkv * hd + nkv * vd;
     const size_t smem = (size_t)(cv.C + rot + vd) * sizeof(float);
     if (smem > 200 * 1024) return CELLM_ERR_SIZE;
-    // a thread about four channels: the convolution's loads of one channel wait on nothing of another's
-    const int threads = cv.C >= 4096 ? 1024 : cv.C >= 2048 ? 512 : 256;
+    // few tokens: a thread about four channels, since a step of single tokens is too few blocks to hide a thread's chain
+    // of loads behind other blocks (the sums of squares are then added in another order: a rounding apart)
+    const int threads = T >= 512 ? 256 : cv.C >= 4096 ? 1024 : cv.C >= 2048 ? 512 : 256;
 #define PREP_RUN(TA)                                                                                                          \
     do {                                                                                                                      \
         if (smem > 48 * 1024) {                                                                                               \
