@@ -153,6 +153,11 @@ class Program:
         kinds = None
         if model is not None and self.all_native:
             kinds = {r.kind for recs in [self.prologue, self.epilogue] + self.layers for r in recs}
+        # a program without records runs parts' records one at a time: a library that only some kinds of record reach
+        # is loaded (and if need be compiled) when the first record of such a kind comes (`run_part`)
+        self._late_kinds = set() if (model is None and entries is None) else None
+        if self._late_kinds is not None:
+            kinds = set()
         for i, addr in enumerate(entries if entries is not None else entry_points(self.dtype, kinds)):
             p.fns[i] = addr
         self._keep += [a, b, per_layer, layer_arr, order_arr]
@@ -256,6 +261,11 @@ class Program:
             if record.kind != R.LINEAR:
                 x = x.to(self.dtype).contiguous()
         p = self.program
+        if self._late_kinds is not None and record.kind not in self._late_kinds:
+            self._late_kinds.add(record.kind)
+            for i, addr in enumerate(entry_points(self.dtype, {record.kind})):
+                if addr and not p.fns[i]:
+                    p.fns[i] = addr
         self._options()
         from ..parts.base import CacheBinding
         if ctx is not None:

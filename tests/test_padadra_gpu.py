@@ -277,6 +277,29 @@ def test_sharp_attention_at_the_window_edges_and_far_back(tmp_path, dtype):
                 against_plain(traces.as_matrix(got[rid], len(t)), ref[rid], dtype, f"sharp {dtype} {fam} page {page} {rid}")
 
 
+@pytest.mark.parametrize("heads", [16, 32])
+def test_many_channels_a_token(tmp_path, heads):
+    """Projections of 2,560 and 4,608 channels: steps of few tokens spread a token's channels over more threads (and the
+    delta rule's over several blocks) than prompt portions do."""
+    config = model_config(96, 64, [par(left(heads, 2, 128, 128, conv=3, window=20, rot=(10000.0, 64, (2.0, 1.0, 4.0, 16))), right(1, 8, 8)),
+                                   delta(heads, 2, 64, 64, 3, ranks=(4, 4))])
+    folder = write_model(tmp_path / "m", config, 12, init=InitSpec_small())
+    cfg, w = load_plain(folder)
+    rng = np.random.default_rng(2)
+    reqs = {"x": rng.integers(0, 96, 530).tolist(), "y": rng.integers(0, 96, 9).tolist()}
+    ref = {rid: Ref(t, cfg, w) for rid, t in reqs.items()}
+    for dtype in ("float32", "bfloat16"):
+        for fam in ("whole", "tail", "mixed"):
+            got = run_trace(folder, dtype, FAMILIES[fam](reqs), 16)
+            for rid, t in reqs.items():
+                against_plain(traces.as_matrix(got[rid], len(t)), ref[rid], dtype, f"wide {heads} {dtype} {fam} {rid}")
+
+
+def InitSpec_small():
+    from cellm_b200.weights import InitSpec
+    return InitSpec(linear_std=0.05, embedding_std=0.08, bias_std=0.1, norm_jitter=0.2)
+
+
 # ------------------------------------------------------------------------------------------ generation
 def check_greedy_tokens(cfg, w, prompt, out, dtype):
     seq = list(prompt) + list(out[:-1])
