@@ -516,10 +516,11 @@ def test_pair_hash_embedding_and_the_first_token():
     assert int(state[2, 0]) == toks[-1]
 
 
-def test_stream_kernels_and_activation():
+@pytest.mark.parametrize("T,H", [(9, 54), (5, 56), (3, 2048), (70, 1100)])
+def test_stream_kernels_and_activation(T, H):
+    """Rows of a width that is and is not a multiple of four (the kernels move four values at a time where they can)."""
     from cellm_b200 import ops
     g = torch.Generator().manual_seed(3)
-    T, H = 9, 54
     x, a, b = (torch.randn(T, H, generator=g) * 3 for _ in range(3))
     w1, w2 = torch.randn(H, generator=g), torch.randn(H, generator=g)
     y1, y2 = ops.norm_pair(x.to(DEV), w1.to(DEV), w2.to(DEV), 1e-5, torch.float32)
@@ -533,6 +534,21 @@ def test_stream_kernels_and_activation():
     torch.testing.assert_close(xs.cpu().double(), x.double() + 0.3 * (a.double() + b.double()), rtol=1e-6, atol=1e-6)
     u = ops.activation(a.to(DEV), "relu2", torch.float32)
     torch.testing.assert_close(u.cpu().double(), torch.relu(a.double()) ** 2, rtol=1e-6, atol=1e-6)
+    # 16-bit activations and weights
+    b1, b2, ab, bb = w1.bfloat16(), w2.bfloat16(), a.bfloat16(), b.bfloat16()
+    y1, y2 = ops.norm_pair(x.to(DEV), b1.to(DEV), b2.to(DEV), 1e-5, torch.bfloat16)
+    torch.testing.assert_close(y1.cpu().double(), plain.rms(x.double(), 1e-5) * b1.double(), rtol=2 ** -7, atol=1e-3)
+    torch.testing.assert_close(y2.cpu().double(), plain.rms(x.double(), 1e-5) * b2.double(), rtol=2 ** -7, atol=1e-3)
+    only, none = ops.norm_pair(x.to(DEV), b1.to(DEV), None, 1e-5, torch.bfloat16)
+    assert none is None and torch.equal(only, y1)
+    out = ops.pair_norm_mean(a.to(DEV), b.to(DEV), w1.to(DEV), w2.to(DEV), 1e-5, torch.bfloat16)
+    torch.testing.assert_close(out.cpu().double(), want, rtol=2 ** -7, atol=1e-3)
+    xs = x.to(DEV).clone()
+    ops.scaled_add2(xs, ab.to(DEV), bb.to(DEV), 0.3)
+    torch.testing.assert_close(xs.cpu().double(), x.double() + 0.3 * (ab.double() + bb.double()), rtol=1e-6, atol=1e-6)
+    xs = x.to(DEV).clone()
+    ops.scaled_add2(xs, ab.to(DEV), None, -1.5)
+    torch.testing.assert_close(xs.cpu().double(), x.double() - 1.5 * ab.double(), rtol=1e-6, atol=1e-6)
 
 
 @pytest.mark.parametrize("M,K,N", [(300, 64, 200), (17, 128, 96), (8, 64, 80), (2048, 256, 1000)])
