@@ -21,15 +21,16 @@ __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-
 // ------------------------------------------------------------------------------------------------ the walk
 // Heads of up to 128 rows. The walk is a chain of dependent steps, token after token, and a head's state is small: one
 // request's walk is bound by the chain's latency, many requests' walks by the instructions issued. A column of S is
-// shared by DIM / ROWS neighbouring lanes, each holding ROWS of its rows in registers (eight for heads of 64 and 128
-// rows, four below: measured, more lanes a column cost more in the sums over the lanes than their warps hide), in
-// groups of four dealt round robin to the lanes, so that the lanes' 16-byte reads of the token's vectors in shared
-// memory are neighbours. A block of eight warps walks 256 / (DIM / ROWS) neighbouring columns of one (request, head).
+// shared by DIM / ROWS neighbouring lanes, each holding ROWS of its rows in registers (the delta rule: eight for heads
+// of 64 and 128 rows, since every token's u waits for a sum over the lanes; HGRN2, whose state waits for no sum: four;
+// measured), in groups of four dealt round robin to the lanes, so that the lanes' 16-byte reads of the token's vectors
+// in shared memory are neighbours. A block of eight warps walks 256 / (DIM / ROWS) neighbouring columns of one (request, head).
 // The tokens' vectors over the rows, the block's entries of v and beta come in chunks of eight tokens through
 // asynchronous copies into three stages of shared memory, two chunks ahead of the one in use: a chunk costs one
-// barrier and no wait for memory, and within a chunk the warps run free, a whole chunk unrolled so that a token's
-// loads and the sums of the token before overlap. Sums over a column's rows are added lane by lane (shuffles) in a
-// fixed order. The block's tile of S goes through shared memory on its way in and out, in rows of whole sectors.
+// barrier and no wait for memory, and within a chunk the warps run free. Sums over a column's rows are added lane by
+// lane (shuffles) in a fixed order; the read-outs of a whole chunk's tokens wait as the lanes' shares and are summed
+// together, step by step, so that a shuffle's latency is paid once a chunk (the same sums in the same order as token
+// by token). The block's tile of S goes through shared memory on its way in and out, in rows of whole sectors.
 // DIM is the next of 16, 32, 64, 128 above the head's rows; the rows beyond are zeros that nothing reads back.
 template <int DIM, int ROWS> struct WalkShape {
     static constexpr int RG = DIM / ROWS;          // lanes a column
@@ -128,8 +129,8 @@ state_walk_kernel(float* __restrict__ o_out, float* __restrict__ state, long lon
     float S[ROWS];
 #pragma unroll
     for (int ii = 0; ii < ROWS; ++ii) S[ii] = tile[((ii >> 2) * RG + r) * 4 + (ii & 3)][cl];
-    // one token: the lane's rows of the column move on, and lane r == 0 of the column writes its read-out
-    auto token = [&](const float* tok, int t) {
+    // one token: the lane's rows of the column move on; returns the lane's share of the column's read-out
+    auto token = [&](const float* tok) -> float {
         const float4* q4 = reinterpret_cast<const float4*>(tok);
         const float v = tok[NV * DIM + cl];
         float o0 = 0.f, o1 = 0.f;
@@ -167,9 +168,10 @@ state_walk_kernel(float* __restrict__ o_out, float* __restrict__ state, long lon
                 o0 = fmaf(S[4 * g + 2], q.z, o0), o1 = fmaf(S[4 * g + 3], q.w, o1);
             }
         }
-        const float o = sum_over_rows<RG>(o0 + o1);
-        if (live && r == 0) o_out[(size_t)t * heads * vd + (size_t)h * vd + j] = o;
+        return o0 + o1;
     };
+    float* o_col = o_out + (size_t)h * vd + j;
+    const size_t o_ld = (size_t)heads * vd;
     for (int c = 0; c < n_chunks; ++c) {
         copy_async_wait<WALK_STAGES - 2>();
         __syncthreads();        // chunk c has arrived for every thread, and every thread has left chunk c - 1
@@ -178,10 +180,28 @@ state_walk_kernel(float* __restrict__ o_out, float* __restrict__ state, long lon
         const float* stage = buf[c % WALK_STAGES];
         const int t0 = start + c * WALK_CHUNK, nt = min(WALK_CHUNK, end - t0);
         if (nt == WALK_CHUNK) {
+            // a whole chunk: the tokens' read-outs wait as the lanes' shares and are summed over the lanes together, step
+            // by step, so that a shuffle's latency is paid once a chunk and not once a token (the same sums in the same order)
+            float share[WALK_CHUNK];
 #pragma unroll
-            for (int tt = 0; tt < WALK_CHUNK; ++tt) token(stage + tt * TOK, t0 + tt);
+            for (int tt = 0; tt < WALK_CHUNK; ++tt) share[tt] = token(stage + tt * TOK);
+#pragma unroll
+            for (int d = 1; d < RG; d <<= 1) {
+                float other[WALK_CHUNK];
+#pragma unroll
+                for (int tt = 0; tt < WALK_CHUNK; ++tt) other[tt] = __shfl_xor_sync(0xffffffffu, share[tt], d);
+#pragma unroll
+                for (int tt = 0; tt < WALK_CHUNK; ++tt) share[tt] += other[tt];
+            }
+            if (live && r == 0) {
+#pragma unroll
+                for (int tt = 0; tt < WALK_CHUNK; ++tt) o_col[(size_t)(t0 + tt) * o_ld] = share[tt];
+            }
         } else {
-            for (int tt = 0; tt < nt; ++tt) token(stage + tt * TOK, t0 + tt);
+            for (int tt = 0; tt < nt; ++tt) {
+                const float o = sum_over_rows<RG>(token(stage + tt * TOK));
+                if (live && r == 0) o_col[(size_t)(t0 + tt) * o_ld] = o;
+            }
         }
     }
     __syncthreads();
@@ -323,8 +343,8 @@ CELLM_API int cellm_hgrn2_scan(float* o_out, float* state, long long slot_stride
               heads, dim, vd, err)
     if (dim <= 16) HGRN2_WALK(16, 4);
     else if (dim <= 32) HGRN2_WALK(32, 4);
-    else if (dim <= 64) HGRN2_WALK(64, 8);
-    else if (dim <= 128) HGRN2_WALK(128, 8);
+    else if (dim <= 64) HGRN2_WALK(64, 4);
+    else if (dim <= 128) HGRN2_WALK(128, 4);
     else {
         const size_t big = (size_t)(2 + 32) * dim * sizeof(float);
         if (big > 48 * 1024) {
@@ -341,12 +361,12 @@ CELLM_API int cellm_hgrn2_scan(float* o_out, float* state, long long slot_stride
 // ------------------------------------------------------------------------------------------------ delta rule: inputs
 // A few blocks a token. proj row: q (kvh x dim), k (kvh x dim), v (heads x vdim) from col0 on, side by side (the
 // convolution's channels in this order), beta's pre-activation at col_b (heads). a2 [T, heads * dim]: the decay's
-// pre-activation without its bias. Writes qk [T, 2 * kvh * dim] (unit q times dim^-1/2, then unit k), v [T, heads * vdim],
+// pre-activation without its bias (rows ld_a2 apart). Writes qk [T, 2 * kvh * dim] (unit q times dim^-1/2, then unit k), v [T, heads * vdim],
 // beta [T, heads], decay [T, heads * dim] = exp(-exp(A_log_h) * softplus(a2 + dt_bias)).
 __global__ void __launch_bounds__(256)
 delta_prep_kernel(float* __restrict__ qk, float* __restrict__ v_out, float* __restrict__ beta, float* __restrict__ decay,
                   ConvTaps cv, long long slot_stride, int n_slots, const float* __restrict__ state_base, int col_b,
-                  const float* __restrict__ a2, const float* __restrict__ dt_bias, const float* __restrict__ A_log,
+                  const float* __restrict__ a2, long long ld_a2, const float* __restrict__ dt_bias, const float* __restrict__ A_log,
                   const int* __restrict__ seq_of_token, const int* __restrict__ cu_seqlens, const int* __restrict__ slot_ids,
                   int heads, int kvh, int dim, int vd, float l2_eps, int* __restrict__ err) {
     extern __shared__ float buf[];      // [warps][dim]: a q or k head of the token
@@ -383,7 +403,7 @@ delta_prep_kernel(float* __restrict__ qk, float* __restrict__ v_out, float* __re
         for (int h = threadIdx.x; h < heads; h += blockDim.x)
             beta[(size_t)t * heads + h] = sigmoidf_(cv.proj[(size_t)t * cv.ld + col_b + h]);
     for (int idx = thread; idx < heads * dim; idx += threads) {
-        const float xa = a2[(size_t)t * heads * dim + idx] + dt_bias[idx];
+        const float xa = a2[(size_t)t * ld_a2 + idx] + dt_bias[idx];
         const float sp = xa > 20.f ? xa : log1pf(expf(xa));
         decay[(size_t)t * heads * dim + idx] = expf(-expf(A_log[idx / dim]) * sp);
     }
@@ -391,7 +411,7 @@ delta_prep_kernel(float* __restrict__ qk, float* __restrict__ v_out, float* __re
 
 CELLM_API int cellm_delta_prep(float* qk, float* v_out, float* beta, float* decay, const float* proj, long long ld, int col0,
                                int col_b, const float* taps, int n_taps, const float* state, long long slot_stride, int n_slots,
-                               const float* a2, const float* dt_bias, const float* A_log, const int* seq_of_token,
+                               const float* a2, long long ld_a2, const float* dt_bias, const float* A_log, const int* seq_of_token,
                                const int* cu_seqlens, const int* slot_ids, int T, int heads, int kvh, int dim, int vd,
                                float l2_eps, int* err, cudaStream_t stream) {
     if (T <= 0) return CELLM_OK;
@@ -404,7 +424,7 @@ CELLM_API int cellm_delta_prep(float* qk, float* v_out, float* beta, float* deca
     // few tokens: a token's channels over as many blocks as leave a thread about four of them (no sum crosses blocks)
     const int widest = std::max(cv.C, heads * dim), parts = T >= 512 ? 1 : std::max(1, std::min((widest + 1023) / 1024, 64));
     CELLM_RUN(delta_prep_kernel, dim3(T, parts), 256, (size_t)8 * dim * sizeof(float), stream, qk, v_out, beta, decay, cv, slot_stride,
-              n_slots, state, col_b, a2, dt_bias, A_log, seq_of_token, cu_seqlens, slot_ids, heads, kvh, dim, vd, l2_eps, err);
+              n_slots, state, col_b, a2, ld_a2, dt_bias, A_log, seq_of_token, cu_seqlens, slot_ids, heads, kvh, dim, vd, l2_eps, err);
     return CELLM_OK;
 }
 

@@ -55,7 +55,7 @@ _SIGNATURES = {
         "cellm_sink_attn_prep": [P, P, P, P, L, I, P, P, I, P, L, I, P, P, F, P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P],
         "cellm_attention_plain_sink": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P, I, I, P, P],
         "cellm_hgrn2_scan": [P, P, L, I, P, L, I, I, I, P, P, P, P, I, I, I, I, I, P, P],
-        "cellm_delta_prep": [P, P, P, P, P, L, I, I, P, I, P, L, I, P, P, P, P, P, P, I, I, I, I, I, F, P, P],
+        "cellm_delta_prep": [P, P, P, P, P, L, I, I, P, I, P, L, I, P, L, P, P, P, P, P, I, I, I, I, I, F, P, P],
         "cellm_delta_scan": [P, P, L, I, P, P, P, P, P, P, I, I, I, I, I, P, P],
         "cellm_head_norm_gate": [P, P, P, P, L, I, I, I, F, I, P],
     },

@@ -166,11 +166,11 @@ def delta_prep(proj: torch.Tensor, col0: int, col_b: int, taps, n_taps: int, con
     v = torch.empty((T, heads * vd), dtype=torch.float32, device=dev)
     beta = torch.empty((T, heads), dtype=torch.float32, device=dev)
     decay = torch.empty((T, heads * dim), dtype=torch.float32, device=dev)
-    if not a2.is_contiguous() or a2.shape != (T, heads * dim):
-        raise ValueError("delta_prep: the decay's pre-activation [T, heads * dim], dense")
+    if a2.stride(1) != 1 or a2.shape != (T, heads * dim):
+        raise ValueError("delta_prep: the decay's pre-activation [T, heads * dim] (rows may be strided)")
     check(fn(_LIB, "cellm_delta_prep")(ptr(qk), ptr(v), ptr(beta), ptr(decay), ptr(proj), proj.stride(0), int(col0), int(col_b), ptr(taps),
                                        int(n_taps), ptr(conv_state), conv_state.stride(0) if conv_state is not None else 0,
-                                       conv_state.shape[0] if conv_state is not None else 1 << 30, ptr(a2), ptr(dt_bias), ptr(A_log),
+                                       conv_state.shape[0] if conv_state is not None else 1 << 30, ptr(a2), a2.stride(0), ptr(dt_bias), ptr(A_log),
                                        ptr(ctx.seq_of_token), ptr(ctx.cu_seqlens), ptr(ctx.slot_ids), T, heads, kvh, dim, vd, float(l2_eps),
                                        ptr(ctx.err), stream_of(proj)), "delta_prep")
     return qk, v, beta, decay

@@ -111,7 +111,14 @@ class GatedDeltaMixer(Mixer):
             raise ConfigError("gated_delta: the two matrices of a low-rank product do not fit each other")
         self.in_proj = Linear(stack_rows(weights["q"], weights["k"], weights["v"], weights["beta"]), dtype)
         self.low_proj = Linear(stack_rows(weights["a1"], weights["g1"]), dtype)
-        self.a2, self.g2 = Linear(weights["a2"], dtype), Linear(weights["g2"], dtype)
+        # the two second halves as one product: a2 and g2 on the diagonal of one matrix over a1's and g1's outputs side by
+        # side (the zeros add nothing to a sum), so the decays' and the gate's pre-activations come from one launch
+        a2, g2 = weights["a2"], weights["g2"]
+        both = torch.zeros((a2.shape[0] + g2.shape[0], self.ra + self.rg), dtype=a2.dtype if a2.dtype == g2.dtype else torch.float32,
+                           device=a2.device)
+        both[:a2.shape[0], :self.ra] = a2
+        both[a2.shape[0]:, self.ra:] = g2
+        self.second = Linear(both, dtype)
         self.out_proj = Linear(weights["o"], dtype)
         self.conv_w = torch.cat([weights[n].to(torch.float32) for n in ("q_conv", "k_conv", "v_conv")], dim=0).contiguous()
         self.dt_bias, self.A_log, self.norm_w = _f32(weights, "dt_bias"), _f32(weights, "A_log"), _f32(weights, "norm")
@@ -124,8 +131,8 @@ class GatedDeltaMixer(Mixer):
         state = b[-1].state
         proj = self.in_proj(x, out_dtype=torch.float32)
         low = self.low_proj(x)
-        a = self.a2(low[:, :self.ra], out_dtype=torch.float32)
-        gate = self.g2(low[:, self.ra:], out_dtype=torch.float32)
+        second = self.second(low, out_dtype=torch.float32)
+        a, gate = second[:, :self.heads * self.dim], second[:, self.heads * self.dim:]
         C = 2 * self.qkh * self.dim + self.heads * self.vd
         qk, v, beta, decay = ops.delta_prep(proj, 0, C, self.conv_w, self.taps, conv_state, a, self.dt_bias, self.A_log, ctx,
                                             self.heads, self.qkh, self.dim, self.vd, self.unit_eps)
