@@ -151,7 +151,7 @@ class Program:
         self._callback = R.PythonOpFn(self._python_op)
         p.python = self._callback
         kinds = None
-        if model is not None and self.all_native:
+        if model is not None:       # parts that run in Python take their own records to a program without records (below)
             kinds = {r.kind for recs in [self.prologue, self.epilogue] + self.layers for r in recs}
         # a program without records runs parts' records one at a time: a library that only some kinds of record reach
         # is loaded (and if need be compiled) when the first record of such a kind comes (`run_part`)
