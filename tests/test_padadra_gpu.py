@@ -551,7 +551,7 @@ def test_stream_kernels_and_activation(T, H):
     torch.testing.assert_close(xs.cpu().double(), x.double() - 1.5 * ab.double(), rtol=1e-6, atol=1e-6)
 
 
-@pytest.mark.parametrize("M,K,N", [(300, 64, 200), (17, 128, 96), (8, 64, 80), (2048, 256, 1000)])
+@pytest.mark.parametrize("M,K,N", [(300, 64, 200), (17, 128, 96), (8, 64, 80), (2048, 256, 1000), (40, 64, 33), (100, 72, 7), (129, 40, 129)])
 def test_product_with_the_activation_in_its_epilogue(M, K, N):
     """Prompt portions under bfloat16 form the feed-forward's activation on the 32-bit sums in the product itself."""
     from cellm_b200 import ops
