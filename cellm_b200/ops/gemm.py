@@ -20,11 +20,12 @@ def gemm_plain(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None =
     return c
 
 
-def gemm(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+def gemm(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None, records: dict | None = None) -> torch.Tensor:
     """The product a [M, K] . w [N, K]^T by the kernel the native executor chooses for the operands: 32-bit
     operands run the plain 32-bit kernel; bfloat16 operands run the tensor-core kernel in the tile shape and K
     split that fit M, N and K (or the plain kernel where K or the rows' alignment do not fit it). `w` is taken
-    for a weight that nothing on the stream writes."""
+    for a weight that nothing on the stream writes. `records`: the caller's dictionary, in which the product's record is
+    kept from call to call (a part that multiplies with the same weight every step)."""
     from ..runtime import records as R
     from ..runtime.program import part_program
     if a.dtype != w.dtype or a.dim() != 2 or w.dim() != 2 or a.shape[1] != w.shape[1] or a.stride(1) != 1 or w.stride(1) != 1:
@@ -33,9 +34,14 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None)
     c = torch.empty((a.shape[0], w.shape[0]), dtype=out_dtype, device=a.device)
     if a.shape[0] == 0:
         return c
-    rec = R.Record(R.LINEAR, R.LinearParams(R.linear(w), a.stride(0), tag(out_dtype)))
-    if a.data_ptr() % 16:
-        rec.params.w.tc_ok = 0
+    key = (a.stride(0), out_dtype, a.data_ptr() % 16 == 0)
+    rec = records.get(key) if records is not None else None
+    if rec is None:
+        rec = R.Record(R.LINEAR, R.LinearParams(R.linear(w), a.stride(0), tag(out_dtype)))
+        if a.data_ptr() % 16:
+            rec.params.w.tc_ok = 0
+        if records is not None:
+            records[key] = rec
     part_program(a.dtype, a.device, a.shape[1]).run_part(rec, a, None, out=c, rows=a.shape[0])
     return c
 
