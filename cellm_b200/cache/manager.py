@@ -79,8 +79,9 @@ class CacheManager:
                                            dtype=need.dtype, device=self.device))
         # A model without paged items (no attention at all) has no page group: its requests hold a slot only.
         windows = [k.window for k in self.paged_keys]
+        keeps = [k.keep_first if k.window else 0 for k in self.paged_keys]
         self._h = lib().cellm_cache_create(self.page_size, n_paged, int_array(self.group_pages), int_array(windows),
-                                           self.num_slots)
+                                           int_array(keeps), self.num_slots)
         if not self._h:
             raise CacheError(last_error())
 

@@ -20,7 +20,7 @@ def lib():
         IP, LP = POINTER(c_int), POINTER(c_longlong)
         sig = {
             "cellm_last_error": ([], c_char_p),
-            "cellm_cache_create": ([c_int, c_int, IP, IP, c_int], c_void_p),
+            "cellm_cache_create": ([c_int, c_int, IP, IP, IP, c_int], c_void_p),
             "cellm_cache_destroy": ([c_void_p], None),
             "cellm_cache_add": ([c_void_p, c_longlong], c_int),
             "cellm_cache_reserve": ([c_void_p, c_longlong, c_int], c_int),

@@ -35,7 +35,7 @@ LIBRARIES: dict[str, tuple[str, list[str], list[str]]] = {
                                 "kernels/qk_norm_rope.cu", "kernels/swiglu.cu", "kernels/sample.cu",
                                 "kernels/attention_plain.cu", "kernels/gated_norm.cu", "kernels/mingru.cu",
                                 "kernels/latent.cu", "kernels/attn_prep.cu", "kernels/routed.cu", "kernels/stream_ops.cu",
-                                "kernels/sink_attn_prep.cu", "kernels/recurrent.cu"], []),
+                                "kernels/sink_attn_prep.cu", "kernels/recurrent.cu", "kernels/stream_norm.cu"], []),
     "gemm_plain": ("nvcc", ["kernels/gemm_plain.cu"], []),
     "gemm_tcgen05": ("nvcc", ["kernels/gemm_tcgen05.cu"], []),
     "attention_flash": ("nvcc", ["kernels/attention_flash.cu"], []),

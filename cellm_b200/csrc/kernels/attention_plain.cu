@@ -23,6 +23,7 @@ attention_plain_kernel(TA* __restrict__ out, const TA* __restrict__ q, const TA*
                        const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
                        int bt_stride, int num_pages, int page_size, int nh, int nkv, int hd, int hdv, int v_row, float scale,
                        int window, const float* __restrict__ sinks, const float* __restrict__ unrot, int interleaved,
+                       int keep_first, float fixed_sink, int has_fixed_sink, const float* __restrict__ gate, long long gate_ld,
                        int* __restrict__ err) {
     constexpr int CH = ATTN_PLAIN_THREADS;
     extern __shared__ float smem[];
@@ -44,12 +45,15 @@ attention_plain_kernel(TA* __restrict__ out, const TA* __restrict__ q, const TA*
 #pragma unroll
     for (int r = 0; r < ATTN_PLAIN_MAX_HD / CH; ++r) acc[r] = 0.f;
     const size_t page_elems = (size_t)nkv * page_size * hd, v_page_elems = (size_t)nkv * page_size * v_row;
-    for (int c0 = (lo / CH) * CH; c0 <= pos; c0 += CH) {
+    // with `keep_first` the first keys of the sequence stay visible behind the window: chunks are walked from key 0
+    // and those that hold neither a kept key nor a key of the window are passed over
+    for (int c0 = keep_first > 0 ? 0 : (lo / CH) * CH; c0 <= pos; c0 += CH) {
+        if (c0 >= keep_first && c0 + CH <= lo) continue;
         __syncthreads();
         {   // page of key c0 + tid
             const int j = c0 + threadIdx.x;
             int p = -1;
-            if (j >= lo && j <= pos) {
+            if ((j >= lo || j < keep_first) && j <= pos) {
                 p = block_table[(size_t)b * bt_stride + j / page_size];
                 if (p < 0 || p >= num_pages) { atomicOr(err, CELLM_DEV_BAD_PAGE); p = -1; }
             }
@@ -95,16 +99,18 @@ attention_plain_kernel(TA* __restrict__ out, const TA* __restrict__ q, const TA*
             }
         }
     }
-    if (sinks) {
-        // a sink: one more term exp(sink_h) in the denominator, with no key and no value
-        const float sk = sinks[h];
+    if (sinks || has_fixed_sink) {
+        // a sink: one more term exp(sink_h) in the denominator, with no key and no value (learned per head, or one
+        // fixed score for all heads)
+        const float sk = sinks ? sinks[h] : fixed_sink;
         const float m_new = fmaxf(m, sk);
         const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
         l = l * corr + expf(sk - m_new);
 #pragma unroll
         for (int r = 0; r < ATTN_PLAIN_MAX_HD / CH; ++r) acc[r] *= corr;
     }
-    const float inv = 1.0f / l;
+    // an output gate: the head's sum times sigmoid of one number per (token, head)
+    const float inv = (gate ? 1.f / (1.f + expf(-gate[(size_t)t * gate_ld + h])) : 1.f) / l;
     if (unrot) {
         // values were cached rotated by their own positions: the sum is turned back by the token's position
         // (pair m by -pos * f_m; f as [hdv/2][2] floats, high part and remainder)
@@ -147,9 +153,11 @@ static int attention_plain_impl(void* out, const void* q, const void* k_pool, co
                                 int bt_stride, int num_pages, int page_size, int T, int nh, int nkv,
                                 int hd, int hdv, int v_row, float scale, int window, int dtype, int* err,
                                 cudaStream_t stream, const float* sinks = nullptr, const float* unrot = nullptr,
-                                int interleaved = 0) {
+                                int interleaved = 0, int keep_first = 0, float fixed_sink = 0.f, int has_fixed_sink = 0,
+                                const float* gate = nullptr, long long gate_ld = 0) {
     if (T <= 0) return CELLM_OK;
     if (unrot && hdv % 2) return CELLM_ERR_SIZE;
+    if (keep_first < 0) return CELLM_ERR_SIZE;
     if (hd > ATTN_PLAIN_MAX_HD || hd <= 0 || hdv <= 0 || hdv > v_row || hdv > ATTN_PLAIN_MAX_HD || nkv <= 0 || nh % nkv) return CELLM_ERR_SIZE;
     // the first hd floats hold the query; the output is turned back in the same place (hdv floats)
     const size_t smem = (size_t)((hd > hdv ? hd : hdv) + 2 * ATTN_PLAIN_THREADS) * sizeof(float);
@@ -157,12 +165,12 @@ static int attention_plain_impl(void* out, const void* q, const void* k_pool, co
     if (dtype == CELLM_F32)
         CELLM_RUN(attention_plain_kernel<float>, grid, ATTN_PLAIN_THREADS, smem, stream,
             (float*)out, (const float*)q, (const float*)k_pool, (const float*)v_pool, positions, seq_of_token,
-            block_table, bt_stride, num_pages, page_size, nh, nkv, hd, hdv, v_row, scale, window, sinks, unrot, interleaved, err);
+            block_table, bt_stride, num_pages, page_size, nh, nkv, hd, hdv, v_row, scale, window, sinks, unrot, interleaved, keep_first, fixed_sink, has_fixed_sink, gate, gate_ld, err);
     else if (dtype == CELLM_BF16)
         CELLM_RUN(attention_plain_kernel<__nv_bfloat16>, grid, ATTN_PLAIN_THREADS, smem, stream,
             (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
             (const __nv_bfloat16*)v_pool, positions, seq_of_token, block_table, bt_stride, num_pages,
-            page_size, nh, nkv, hd, hdv, v_row, scale, window, sinks, unrot, interleaved, err);
+            page_size, nh, nkv, hd, hdv, v_row, scale, window, sinks, unrot, interleaved, keep_first, fixed_sink, has_fixed_sink, gate, gate_ld, err);
     else return CELLM_ERR_DTYPE;
     return CELLM_OK;
 }
@@ -199,4 +207,20 @@ CELLM_API int cellm_attention_plain_sink(void* out, const void* q, const void* k
                                          int interleaved, int dtype, int* err, cudaStream_t stream) {
     return attention_plain_impl(out, q, k_pool, v_pool, positions, seq_of_token, block_table, bt_stride, num_pages, page_size, T, nh, nkv,
                                 hd, hdv, hdv, scale, window, dtype, err, stream, sinks, unrot, interleaved);
+}
+
+// The general form: a window that keeps the sequence's first `keep_first` keys visible (position i sees j <= i with
+// i - j < window or j < keep_first; window 0: every earlier key), a learned sink per head (`sinks`) or one fixed sink
+// score for all heads (`has_fixed_sink`), an output gate (`gate` [T, gate_ld] 32-bit pre-activations, one per head: the
+// head's output is multiplied by its sigmoid; null: none), and value rows `v_row` wide of which the first hdv entries are
+// the value (v_pool may be k_pool for a cache whose rows serve as both).
+CELLM_API int cellm_attention_plain_masked(void* out, const void* q, const void* k_pool, const void* v_pool,
+                                           const int* positions, const int* seq_of_token, const int* block_table,
+                                           int bt_stride, int num_pages, int page_size, int T, int nh, int nkv,
+                                           int hd, int hdv, int v_row, float scale, int window, int keep_first,
+                                           const float* sinks, float fixed_sink, int has_fixed_sink, const float* gate,
+                                           long long gate_ld, int dtype, int* err, cudaStream_t stream) {
+    return attention_plain_impl(out, q, k_pool, v_pool, positions, seq_of_token, block_table, bt_stride, num_pages, page_size, T, nh, nkv,
+                                hd, hdv, v_row, scale, window, dtype, err, stream, sinks, nullptr, 0, keep_first, fixed_sink, has_fixed_sink,
+                                gate, gate_ld);
 }

@@ -52,13 +52,14 @@ __device__ __forceinline__ void split_sincos(float fp, float hi, float lo, float
     *s_out = s * ce + c * se;
 }
 
-// Activations by number: 0 gelu (exact), 1 gelu (tanh form), 2 silu, 3 relu, 4 the square of relu.
+// Activations by number: 0 gelu (exact), 1 gelu (tanh form), 2 silu, 3 relu, 4 the square of relu, 5 tanh.
 __device__ __forceinline__ float cellm_activate(float z, int act) {
     switch (act) {
         case 0: return 0.5f * z * (1.f + erff(z * 0.70710678118654752f));                    // gelu, exact
         case 1: return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));   // gelu, tanh form
         case 2: return z / (1.f + expf(-z));                                                 // silu
         case 4: { const float r = fmaxf(z, 0.f); return r * r; }                              // relu, squared
+        case 5: return tanhf(z);
         default: return fmaxf(z, 0.f);                                                       // relu
     }
 }

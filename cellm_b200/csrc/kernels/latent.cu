@@ -34,7 +34,7 @@ latent_prep_kernel(TA* __restrict__ q_plain, TA* __restrict__ q_full, const TP* 
                    const TW* __restrict__ c_norm_w, float eps, const int* __restrict__ positions,
                    const int* __restrict__ seq_of_token, const int* __restrict__ block_table, int bt_stride,
                    TA* __restrict__ pool, int num_pages, int page_size, int heads, int dim, int rot_dim, int rank,
-                   int rot, const float* __restrict__ inv_freq, int* __restrict__ err) {
+                   int rot, int interleaved, const float* __restrict__ inv_freq, int* __restrict__ err) {
     extern __shared__ float smem[];
     float* cs = smem;                // [rot/2]
     float* sn = smem + rot / 2;      // [rot/2]
@@ -72,9 +72,12 @@ latent_prep_kernel(TA* __restrict__ q_plain, TA* __restrict__ q_full, const TP* 
         const TP* src = row + h * qw + dim;
         float v = to_float(src[d]);
         if (d < rot) {
-            const int p = d >> 1;
-            const float other = to_float(src[d ^ 1]);
-            v = (d & 1) ? v * cs[p] + other * sn[p] : v * cs[p] - other * sn[p];
+            // pairs (2p, 2p + 1) when interleaved, (p, p + rot/2) otherwise; the pair's first entry is u cos - v sin
+            const int half = rot >> 1;
+            const int p = interleaved ? d >> 1 : (d < half ? d : d - half);
+            const bool second = interleaved ? (d & 1) : d >= half;
+            const float other = to_float(src[interleaved ? d ^ 1 : (second ? d - half : d + half)]);
+            v = second ? v * cs[p] + other * sn[p] : v * cs[p] - other * sn[p];
         }
         q_full[((size_t)t * heads + h) * kw + rank + d] = from_float<TA>(v);
     }
@@ -95,9 +98,11 @@ latent_prep_kernel(TA* __restrict__ q_plain, TA* __restrict__ q_full, const TP* 
         for (int d = threadIdx.x; d < rot_dim; d += blockDim.x) {
             float v = to_float(down[rank + d]);
             if (d < rot) {
-                const int p = d >> 1;
-                const float other = to_float(down[rank + (d ^ 1)]);
-                v = (d & 1) ? v * cs[p] + other * sn[p] : v * cs[p] - other * sn[p];
+                const int half = rot >> 1;
+                const int p = interleaved ? d >> 1 : (d < half ? d : d - half);
+                const bool second = interleaved ? (d & 1) : d >= half;
+                const float other = to_float(down[rank + (interleaved ? d ^ 1 : (second ? d - half : d + half))]);
+                v = second ? v * cs[p] + other * sn[p] : v * cs[p] - other * sn[p];
             }
             cache_row[rank + d] = from_float<TA>(v);
         }
@@ -107,11 +112,12 @@ latent_prep_kernel(TA* __restrict__ q_plain, TA* __restrict__ q_full, const TP* 
 // proj: [T, ld] = [heads * (dim + rot_dim) queries | kv_rank latent | rot_dim shared key part] (32-bit, or the
 // activations' type); q_plain: [T, heads * dim]; q_full: [T, heads, kv_rank + rot_dim] (only the last rot_dim of each
 // head are written); pool: one layer's rows or null (the item reads another's cache). rot: how many of the rot_dim
-// values turn (even); inv_freq: [rot / 2] pairs of floats (frequency, remainder).
+// values turn (even), in pairs (2p, 2p + 1) if `interleaved`, else (p, p + rot / 2); inv_freq: [rot / 2] pairs of floats
+// (frequency, remainder).
 CELLM_API int cellm_latent_prep(void* q_plain, void* q_full, const void* proj, long long ld, int proj_dtype, const void* c_norm_w,
                                 int w_dtype, float eps, const int* positions, const int* seq_of_token, const int* block_table,
                                 int bt_stride, void* pool, int num_pages, int page_size, int T, int heads, int dim, int rot_dim,
-                                int rank, int rot, const float* inv_freq, int act_dtype, int* err, cudaStream_t stream) {
+                                int rank, int rot, int interleaved, const float* inv_freq, int act_dtype, int* err, cudaStream_t stream) {
     if (T <= 0) return CELLM_OK;
     if (heads <= 0 || dim < 0 || rot_dim < 0 || rank <= 0 || rot < 0 || rot > rot_dim || (rot & 1)) return CELLM_ERR_SIZE;
     if (ld < (long long)heads * (dim + rot_dim) + rank + rot_dim) return CELLM_ERR_SIZE;
@@ -124,7 +130,7 @@ CELLM_API int cellm_latent_prep(void* q_plain, void* q_full, const void* proj, l
 #define LAUNCH(TP, TA, TW)                                                                                              \
     CELLM_RUN((latent_prep_kernel<TP, TA, TW>), grid, 128, smem, stream, (TA*)q_plain, (TA*)q_full, (const TP*)proj, ld,    \
               (const TW*)c_norm_w, eps, positions, seq_of_token, block_table, bt_stride, (TA*)pool, num_pages, page_size, \
-              heads, dim, rot_dim, rank, rot, inv_freq, err)
+              heads, dim, rot_dim, rank, rot, interleaved, inv_freq, err)
     if (act_dtype == CELLM_F32 && proj_dtype == CELLM_F32 && w_dtype == CELLM_F32) LAUNCH(float, float, float);
     else if (act_dtype == CELLM_F32 && proj_dtype == CELLM_F32 && w_dtype == CELLM_BF16) LAUNCH(float, float, __nv_bfloat16);
     else if (act_dtype == CELLM_BF16 && proj_dtype == CELLM_F32 && w_dtype == CELLM_BF16) LAUNCH(float, __nv_bfloat16, __nv_bfloat16);

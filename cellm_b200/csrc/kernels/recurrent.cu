@@ -2,6 +2,7 @@
 //
 //   HGRN2            S <- diag(f) S + (1 - f) v^T                      o = S^T q
 //   gated delta rule S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+//   generalized delta rule   S <- diag(d) S - (a * u)(u^T S) + k v^T (the old S on the right)   o = S^T r
 //
 // In both, column j of S needs only v_j (and the token's vectors over the rows), so the columns are independent: a
 // block walks some neighbouring columns of one (request, head) through the request's tokens of the step in order,
@@ -519,12 +520,126 @@ CELLM_API int cellm_delta_scan(float* o_out, float* state, long long slot_stride
     return CELLM_OK;
 }
 
+// ------------------------------------------------------------------------------------------------ generalized delta rule
+// S <- diag(d) S - (a * u)(u^T S) + k v^T, where both the decay and the removal read the old S; o = S^T r.
+//   d = exp(-c * sigmoid(w_pre + w0))   a decay per head and key channel, c a constant of the design
+//   a = sigmoid(a_pre + a_bias)         a removal rate per head and key channel
+//   u = k / sqrt(sum(k^2) + unit_eps)   the unit key of each head
+// The inputs' kernel forms d, u and a * u for every token (a warp a head); the walk reads r, k, v from the projection.
+__global__ void __launch_bounds__(256)
+gdelta_prep_kernel(float* __restrict__ vecs, const float* __restrict__ proj, long long ld, int col_k, int col_a,
+                   const float* __restrict__ w_pre, long long ld_w, const float* __restrict__ w0, const float* __restrict__ a_bias,
+                   float c, float unit_eps, int heads, int dim) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5, HD = heads * dim;
+    const float* row = proj + t * ld;
+    float* out = vecs + t * 3 * HD;
+    for (int h = warp; h < heads; h += nwarps) {
+        float ss = 0.f;
+        for (int i = lane; i < dim; i += 32) {
+            const float k = row[col_k + h * dim + i];
+            ss = fmaf(k, k, ss);
+        }
+        ss = warp_sum(ss);
+        const float inv = 1.f / sqrtf(ss + unit_eps);
+        for (int i = lane; i < dim; i += 32) {
+            const int ch = h * dim + i;
+            const float u = row[col_k + ch] * inv;
+            const float a = sigmoidf_(row[col_a + ch] + a_bias[ch]);
+            out[ch] = expf(-c * sigmoidf_(w_pre[t * ld_w + ch] + w0[ch]));
+            out[HD + ch] = u;
+            out[2 * HD + ch] = a * u;
+        }
+    }
+}
+
+// vecs [T, 3, heads * dim] 32-bit: decay | unit key | removal rate times unit key.
+CELLM_API int cellm_gdelta_prep(float* vecs, const float* proj, long long ld, int col_k, int col_a, const float* w_pre, long long ld_w,
+                                const float* w0, const float* a_bias, float c, float unit_eps, int T, int heads, int dim,
+                                cudaStream_t stream) {
+    if (T <= 0) return CELLM_OK;
+    if (heads <= 0 || dim <= 0) return CELLM_ERR_SIZE;
+    CELLM_RUN(gdelta_prep_kernel, T, 256, 0, stream, vecs, proj, ld, col_k, col_a, w_pre, ld_w, w0, a_bias, c, unit_eps, heads, dim);
+    return CELLM_OK;
+}
+
+// The walk, a warp a (request, head, 32 columns of S): the columns in shared memory, one lane a column. Every sum
+// runs over the head's rows in order, so the state after a token does not depend on how the sequence was cut.
+__global__ void __launch_bounds__(32)
+gdelta_scan_kernel(float* __restrict__ o_out, float* __restrict__ state, long long slot_stride, int n_slots,
+                   const float* __restrict__ proj, long long ld, int col_r, int col_k, int col_v, const float* __restrict__ vecs,
+                   const int* __restrict__ cu_seqlens, const int* __restrict__ slot_ids, int heads, int dim, int vd,
+                   int* __restrict__ err) {
+    extern __shared__ float sm[];
+    float* rs = sm;                 // [dim] each: r, k, decay, u, a * u
+    float* ks = sm + dim;
+    float* ds = sm + 2 * dim;
+    float* us = sm + 3 * dim;
+    float* as = sm + 4 * dim;
+    float* Ssh = sm + 5 * dim;      // [dim][32]: the warp's columns of S
+    const int b = blockIdx.x, h = blockIdx.y, lane = threadIdx.x, j = blockIdx.z * 32 + lane;
+    auto S = [&](int i) -> float& { return Ssh[i * 32 + lane]; };
+    pdl_trigger();
+    pdl_wait();
+    const int slot = slot_ids[b];
+    if (slot < 0 || slot >= n_slots) { if (lane == 0) atomicOr(err, CELLM_DEV_BAD_SLOT); return; }
+    const int start = cu_seqlens[b], end = cu_seqlens[b + 1], HD = heads * dim;
+    float* st = state + (size_t)slot * slot_stride + (size_t)h * dim * vd;
+    const bool live = j < vd;
+    for (int i = 0; i < dim; ++i) S(i) = live ? st[(size_t)i * vd + j] : 0.f;
+    for (int t = start; t < end; ++t) {
+        const float* row = proj + (size_t)t * ld;
+        const float* vt = vecs + (size_t)t * 3 * HD + h * dim;
+        for (int i = lane; i < dim; i += 32) {
+            rs[i] = row[col_r + h * dim + i];
+            ks[i] = row[col_k + h * dim + i];
+            ds[i] = vt[i];
+            us[i] = vt[HD + i];
+            as[i] = vt[2 * HD + i];
+        }
+        const float v = live ? row[col_v + h * vd + j] : 0.f;
+        __syncwarp();
+        float dot = 0.f;
+        for (int i = 0; i < dim; ++i) dot = fmaf(us[i], S(i), dot);
+        float o = 0.f;
+        for (int i = 0; i < dim; ++i) {
+            const float s_new = fmaf(ks[i], v, fmaf(ds[i], S(i), -as[i] * dot));
+            S(i) = s_new;
+            o = fmaf(s_new, rs[i], o);
+        }
+        if (live) o_out[(size_t)t * heads * vd + (size_t)h * vd + j] = o;
+        __syncwarp();
+    }
+    if (live)
+        for (int i = 0; i < dim; ++i) st[(size_t)i * vd + j] = S(i);
+}
+
+// proj [T, ld] 32-bit holds r (heads x dim) at col_r, k at col_k, v (heads x vd) at col_v; vecs as gdelta_prep left them;
+// state [slots][heads][dim][vd] is moved on; o_out [T, heads * vd] gets S^T r (not normed).
+CELLM_API int cellm_gdelta_scan(float* o_out, float* state, long long slot_stride, int n_slots, const float* proj, long long ld,
+                                int col_r, int col_k, int col_v, const float* vecs, const int* cu_seqlens, const int* slot_ids,
+                                int B, int heads, int dim, int vd, int* err, cudaStream_t stream) {
+    if (B <= 0) return CELLM_OK;
+    if (heads <= 0 || dim <= 0 || vd <= 0 || dim > RECURRENT_MAX_DIM) return CELLM_ERR_SIZE;
+    const size_t smem = (size_t)(5 + 32) * dim * sizeof(float);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(gdelta_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    CELLM_RUN(gdelta_scan_kernel, dim3(B, heads, (vd + 31) / 32), 32, smem, stream, o_out, state, slot_stride, n_slots, proj, ld, col_r,
+              col_k, col_v, vecs, cu_seqlens, slot_ids, heads, dim, vd, err);
+    return CELLM_OK;
+}
+
 // ------------------------------------------------------------------------------------------------ norm over a head's output
-// out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * w[:] (* sigmoid(gate[t, h, :])): a warp a (token, head).
+// out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * w[:] (* sigmoid(gate[t, h, :])): a warp a (token, head). w is one row
+// of vd values for all heads, or (w_per_head) a row for every head.
 template <typename TA>
 __global__ void __launch_bounds__(256)
 head_norm_gate_kernel(TA* __restrict__ out, const float* __restrict__ o, const float* __restrict__ w,
-                      const float* __restrict__ gate, long long gate_ld, int n_rows, int heads, int vd, float eps) {
+                      const float* __restrict__ gate, long long gate_ld, int n_rows, int heads, int vd, float eps, int w_per_head) {
     pdl_trigger();
     pdl_wait();
     const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -535,23 +650,24 @@ head_norm_gate_kernel(TA* __restrict__ out, const float* __restrict__ o, const f
     ss = warp_sum(ss);
     const float inv = 1.f / sqrtf(ss / (float)vd + eps);
     const int t = r / heads, h = r % heads;
+    const float* wr = w + (w_per_head ? (size_t)h * vd : 0);
     for (int j = lane; j < vd; j += 32) {
-        float y = x[j] * inv * w[j];
+        float y = x[j] * inv * wr[j];
         if (gate) y *= sigmoidf_(gate[(size_t)t * gate_ld + (size_t)h * vd + j]);
         out[(size_t)r * vd + j] = from_float<TA>(y);
     }
 }
 
 CELLM_API int cellm_head_norm_gate(void* out, const float* o, const float* w, const float* gate, long long gate_ld, int T,
-                                   int heads, int vd, float eps, int dtype, cudaStream_t stream) {
+                                   int heads, int vd, float eps, int w_per_head, int dtype, cudaStream_t stream) {
     if (T <= 0) return CELLM_OK;
     if (heads <= 0 || vd <= 0) return CELLM_ERR_SIZE;
     const int n_rows = T * heads;
     const unsigned blocks = (unsigned)((n_rows + 7) / 8);
     if (dtype == CELLM_F32)
-        CELLM_RUN(head_norm_gate_kernel<float>, blocks, 256, 0, stream, (float*)out, o, w, gate, gate_ld, n_rows, heads, vd, eps);
+        CELLM_RUN(head_norm_gate_kernel<float>, blocks, 256, 0, stream, (float*)out, o, w, gate, gate_ld, n_rows, heads, vd, eps, w_per_head);
     else if (dtype == CELLM_BF16)
-        CELLM_RUN(head_norm_gate_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, o, w, gate, gate_ld, n_rows, heads, vd, eps);
+        CELLM_RUN(head_norm_gate_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, o, w, gate, gate_ld, n_rows, heads, vd, eps, w_per_head);
     else return CELLM_ERR_DTYPE;
     return CELLM_OK;
 }

@@ -378,7 +378,7 @@ __global__ void activation_kernel(T* __restrict__ h, const float* __restrict__ u
 
 CELLM_API int cellm_activation(void* h, const float* u, long long ld, int T, int n, int act, int dtype, cudaStream_t stream) {
     if (T <= 0 || n <= 0) return CELLM_OK;
-    if (act < 0 || act > 4) return CELLM_ERR_ARG;
+    if (act < 0 || act > 5) return CELLM_ERR_ARG;
     const size_t total = (size_t)T * n;
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (dtype == CELLM_F32) CELLM_RUN(activation_kernel<float>, blocks, 256, 0, stream, (float*)h, u, ld, n, act, total);

@@ -20,7 +20,7 @@ sink_attn_prep_kernel(TA* __restrict__ q_out, TA* __restrict__ k_pool, TA* __res
                       const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                       const int* __restrict__ cu_seqlens, const int* __restrict__ slot_ids,
                       const int* __restrict__ block_table, int bt_stride, int num_pages, int page_size,
-                      int nh, int nkv, int hd, int vd, int* __restrict__ err) {
+                      int nh, int nkv, int hd, int vd, const float* __restrict__ q_mult, int* __restrict__ err) {
     extern __shared__ float sm[];
     const int Cq = nh * hd, Ck = nkv * hd, Cv = nkv * vd, C = Cq + Ck + Cv;
     float* buf = sm;                       // [C]
@@ -78,7 +78,8 @@ sink_attn_prep_kernel(TA* __restrict__ q_out, TA* __restrict__ k_pool, TA* __res
         }
     }
     __syncthreads();
-    for (int c = threadIdx.x; c < Cq; c += blockDim.x) q_out[(size_t)t * Cq + c] = from_float<TA>(buf[c]);
+    // q_mult: one factor per query head (a learned temperature of the head's scores), applied in 32-bit
+    for (int c = threadIdx.x; c < Cq; c += blockDim.x) q_out[(size_t)t * Cq + c] = from_float<TA>(q_mult ? buf[c] * q_mult[c / hd] : buf[c]);
     if (page_ok) {
         const int in_page = pos % page_size;
         for (int c = threadIdx.x; c < Ck; c += blockDim.x) {
@@ -94,14 +95,14 @@ sink_attn_prep_kernel(TA* __restrict__ q_out, TA* __restrict__ k_pool, TA* __res
 
 // proj [T, ld] 32-bit: q (nh x hd), k (nkv x hd), v (nkv x vd) from col0 on; bias, taps [C, n_taps] and the state
 // [slots][n_taps - 1][C] follow the same order of channels. q_norm_w / k_norm_w: null for no norm. qk_freq [rot/2][2],
-// v_freq [vd/2][2] (null: values are not rotated). q_out [T, nh * hd]; pools [page][kv head][slot in page][hd | vd].
+// v_freq [vd/2][2] (null: values are not rotated). q_mult [nh]: a factor per query head (null: none). q_out [T, nh * hd]; pools [page][kv head][slot in page][hd | vd].
 CELLM_API int cellm_sink_attn_prep(void* q_out, void* k_pool, void* v_pool, const float* proj, long long ld, int col0,
                                    const float* bias, const float* taps, int n_taps, const float* state, long long slot_stride,
                                    int n_slots, const float* q_norm_w, const float* k_norm_w, float eps, const float* qk_freq,
                                    int rot, const float* v_freq, int interleaved, const int* positions, const int* seq_of_token,
                                    const int* cu_seqlens, const int* slot_ids, const int* block_table, int bt_stride,
-                                   int num_pages, int page_size, int T, int nh, int nkv, int hd, int vd, int dtype, int* err,
-                                   cudaStream_t stream) {
+                                   int num_pages, int page_size, int T, int nh, int nkv, int hd, int vd, const float* q_mult,
+                                   int dtype, int* err, cudaStream_t stream) {
     if (T <= 0) return CELLM_OK;
     if (nh <= 0 || nkv <= 0 || nh % nkv || hd <= 0 || vd <= 0 || rot < 0 || rot > hd || rot % 2 || (v_freq && vd % 2) ||
         n_taps > CONV_TAPS_MAX || page_size <= 0)
@@ -123,7 +124,7 @@ CELLM_API int cellm_sink_attn_prep(void* q_out, void* k_pool, void* v_pool, cons
         }                                                                                                                     \
         CELLM_RUN(sink_attn_prep_kernel<TA>, T, threads, smem, stream, (TA*)q_out, (TA*)k_pool, (TA*)v_pool, cv, state, slot_stride, \
                   n_slots, q_norm_w, k_norm_w, eps, qk_freq, rot, v_freq, interleaved, positions, seq_of_token, cu_seqlens, \
-                  slot_ids, block_table, bt_stride, num_pages, page_size, nh, nkv, hd, vd, err);                             \
+                  slot_ids, block_table, bt_stride, num_pages, page_size, nh, nkv, hd, vd, q_mult, err);                             \
     } while (0)
     if (dtype == CELLM_F32) PREP_RUN(float);
     else if (dtype == CELLM_BF16) PREP_RUN(__nv_bfloat16);

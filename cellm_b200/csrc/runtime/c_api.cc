@@ -34,10 +34,11 @@ int guarded(F&& f) {
 API const char* cellm_last_error() { return g_error.c_str(); }
 
 // ------------------------------------------------------------------ cache
-API void* cellm_cache_create(int page_size, int n_groups, const int* pages, const int* windows, int num_slots) {
+// keep_first: per group, how many of a sequence's first keys stay readable behind the window (null: none anywhere)
+API void* cellm_cache_create(int page_size, int n_groups, const int* pages, const int* windows, const int* keep_first, int num_slots) {
     try {
         std::vector<cellm::GroupSpec> groups;
-        for (int g = 0; g < n_groups; ++g) groups.push_back({pages[g], windows[g]});
+        for (int g = 0; g < n_groups; ++g) groups.push_back({pages[g], windows[g], keep_first ? keep_first[g] : 0});
         return new cellm::CacheManager(page_size, std::move(groups), num_slots);
     } catch (const std::exception& e) {
         g_error = e.what();

@@ -9,7 +9,7 @@ CacheManager::CacheManager(int page_size, std::vector<GroupSpec> groups, int num
     : page_size_(page_size), groups_(std::move(groups)), slots_(num_slots) {
     if (page_size <= 0) throw CacheError("cache: page size must be positive");
     for (const auto& g : groups_) {
-        if (g.window < 0) throw CacheError("cache: a window must not be negative");
+        if (g.window < 0 || g.keep_first < 0) throw CacheError("cache: a window and its kept first keys must not be negative");
         allocs_.push_back(std::make_unique<BlockAllocator>(g.num_pages));
     }
 }
@@ -81,6 +81,8 @@ void CacheManager::commit(int64_t id, int new_total) {
         if (w <= 0) continue;
         // The next token sits at position >= tokens and reads keys >= tokens - w + 1.
         const int first_key = rc.tokens - w + 1;
+        // pages that hold one of the kept first keys are never given back
+        rc.first_live[g] = std::max(rc.first_live[g], std::min(blocks_for(groups_[g].keep_first), (int)rc.blocks[g].size()));
         while (rc.first_live[g] < (int)rc.blocks[g].size() &&
                (rc.first_live[g] + 1) * page_size_ <= first_key) {
             int32_t& p = rc.blocks[g][(size_t)rc.first_live[g]];
@@ -108,7 +110,8 @@ int CacheManager::pages_for(int g, int tokens, int portion) const {
     // Live keys span at most window - 1 earlier keys plus one portion, and may
     // straddle page edges at both ends.
     const int span = std::min(tokens, w - 1 + std::max(1, portion));
-    return std::min(blocks_for(tokens), blocks_for(span) + 1);
+    const int kept = blocks_for(std::min(tokens, groups_.at((size_t)g).keep_first));
+    return std::min(blocks_for(tokens), blocks_for(span) + 1 + kept);
 }
 
 }  // namespace cellm

@@ -22,6 +22,7 @@ namespace cellm {
 struct GroupSpec {
     int num_pages;
     int window;  // 0: every key is kept; w > 0: a token reads only the last w keys (itself included)
+    int keep_first = 0;  // with a window: the sequence's first keep_first keys stay readable, so their pages are kept
 };
 
 struct RequestCache {

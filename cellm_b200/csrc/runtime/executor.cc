@@ -47,7 +47,10 @@ typedef int (*MinGruScanFn)(P out, CP proj, i64 ld, int proj_tag, CP bz, CP bx, 
                             int T, int B, int W, int n_slots, int max_q_len, int act_tag, P err, P stream);
 typedef int (*LatentPrepFn)(P q_plain, P q_full, CP proj, i64 ld, int proj_tag, CP c_norm_w, int w_tag, float eps, CP positions, CP seq,
                             CP bt, int bt_stride, P pool, int pages, int page_size, int T, int heads, int dim, int rot_dim, int rank,
-                            int rot, CP inv_freq, int act_tag, P err, P stream);
+                            int rot, int interleaved, CP inv_freq, int act_tag, P err, P stream);
+typedef int (*AttentionPlainMaskedFn)(P out, CP q, CP kp, CP vp, CP positions, CP seq, CP bt, int bt_stride, int pages, int page_size,
+                                      int T, int nh, int nkv, int hd, int hdv, int v_row, float scale, int window, int keep_first,
+                                      CP sinks, float fixed_sink, int has_fixed_sink, CP gate, i64 gate_ld, int tag, P err, P stream);
 typedef int (*HeadProductFn)(P out, i64 ldo, i64 out_hs, CP in, i64 ldi, i64 in_hs, CP w, int T, int heads, int N, int K, int tag, P stream);
 typedef int (*GatedActFn)(P h, CP gu, i64 ld, CP bg, CP bu, int w_tag, int T, int ff, int act, int tag, int gu_tag, P stream);
 typedef int (*BiasAddFn)(P out, CP in, CP b, int w_tag, int T, int N, int tag, P stream);
@@ -281,7 +284,12 @@ struct Run {
         product(regs.logits, input(), h.w, s.R, p.H, EXEC_F32);
     }
     void python(const PythonParams& py) {
-        if (dry) return;
+        if (dry) {
+            // the sizing walk calls no Python part: a native part behind one (a head behind a Python norm) finds an
+            // address that stands for the activations the part will leave (never read in this walk)
+            if (!regs.y) regs.y = arena.base;
+            return;
+        }
         if (!p.python) throw std::runtime_error("executor: a Python part in a program without a callback");
         one_addend();
         stream_in_y = false;
@@ -788,7 +796,7 @@ void Run::latent_attention(const LatentAttentionParams& L, const ExecItem& it, c
     LAUNCH(fn<LatentPrepFn>(FN_LATENT_PREP)(q_plain, q_full, proj, L.in_proj.N, (int)act, L.c_norm_w, (int)L.c_norm_dtype, (float)L.eps,
                                         s.positions, s.seq_of_token, it.block_table, (int)it.bt_stride, it.writes ? it.k : nullptr,
                                         (int)it.num_pages, (int)it.page_size, (int)T, (int)nh, (int)L.dim, (int)L.rot_dim, (int)L.rank,
-                                        (int)L.rot, L.inv_freq, (int)act, s.err, s.stream),
+                                        (int)L.rot, (int)L.interleaved, L.inv_freq, (int)act, s.err, s.stream),
            "latent_prep");
     // a head's query against the cached rows: [K_h^T q_h | rotated part]
     head_products(q_full, nh * kw, kw, q_plain, nh * L.dim, L.dim, L.absorb_k, T, nh, L.rank, L.dim);
@@ -803,7 +811,7 @@ void Run::latent_attention(const LatentAttentionParams& L, const ExecItem& it, c
     else if (L.rank % 32 == 0 && L.rank / 32 <= 8) dvw = 32;
     else if (L.rank % 16 == 0 && L.rank / 16 <= 8) dvw = 16;
     const i64 bn = dvw == 256 ? ((64 + 128) * (kw + 8) * 2 + 2048 <= 227 * 1024 ? 64 : 32) : (dvw == 64 ? 64 : 32);
-    if (p.latent_tc && act == EXEC_BF16 && L.scale > 0 && dvw && kw % 16 == 0 && (64 + 2 * bn) * (kw + 8) * 2 + 2048 <= 227 * 1024) {
+    if (p.latent_tc && act == EXEC_BF16 && L.scale > 0 && !L.window && !L.sinks && dvw && kw % 16 == 0 && (64 + 2 * bn) * (kw + 8) * 2 + 2048 <= 227 * 1024) {
         i64 n_tiles = 0;
         for (i64 b = 0; b < s.B; ++b) n_tiles += ceil_div(s.q_lens[b] * nh, 64);
         const i64 blocks = ceil_div(s.max_total_len, bn);
@@ -826,7 +834,13 @@ void Run::latent_attention(const LatentAttentionParams& L, const ExecItem& it, c
                                                       s.err, s.stream),
                "attention_latent");
         if (nsplit > 1) ++launches;                    // the merge of the pieces
-    } else
+    } else if (L.window || L.sinks)
+    LAUNCH(fn<AttentionPlainMaskedFn>(FN_ATTENTION_PLAIN_MASKED)(o_lat, q_full, it.k, it.k, s.positions, s.seq_of_token, it.block_table,
+                                                             (int)it.bt_stride, (int)it.num_pages, (int)it.page_size, (int)T, (int)nh, 1,
+                                                             (int)kw, (int)L.rank, (int)kw, (float)L.scale, (int)L.window, 0, L.sinks, 0.f, 0,
+                                                             nullptr, 0, (int)act, s.err, s.stream),
+           "attention_plain_masked");
+    else
     LAUNCH(fn<AttentionPlainFn>(FN_ATTENTION_PLAIN)(o_lat, q_full, it.k, it.k, s.positions, s.seq_of_token, it.block_table, (int)it.bt_stride,
                                                 (int)it.num_pages, (int)it.page_size, (int)T, (int)nh, 1, (int)kw, (int)L.rank,
                                                 (float)L.scale, 0, (int)act, s.err, s.stream),

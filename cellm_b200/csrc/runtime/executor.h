@@ -113,6 +113,9 @@ struct LatentAttentionParams {
     const void* c_norm_w; i64 c_norm_dtype; double eps;
     i64 rot; const void* inv_freq;
     i64 extra;
+    i64 interleaved;            // the rotation's pairs: (2p, 2p + 1), or (p, p + rot / 2)
+    i64 window;                 // 0: every earlier row; w: a token reads its last w rows
+    const void* sinks;          // [heads] 32-bit: one more term exp(sink_h) in a head's denominator; null: none
 };
 // down . (act(gate . y + bg) * (up . y + bu)) + bd; act 0 silu, 1 gelu (tanh form); the biases may be null.
 struct GatedMlpParams { ExecLinear gate_up, down; const void* bg; const void* bu; const void* bd; i64 b_dtype, ff, act, extra; };
@@ -149,7 +152,7 @@ enum ExecFn {
     FN_ATTENTION_DECODE, FN_ATTENTION_TC, FN_ATTENTION_FLASH, FN_GEMM_TCGEN05, FN_GEMM_CONV, FN_GEMM_ROPE,
     FN_GATED_NORM_ADD, FN_STREAM_CAST, FN_MINGRU_SCAN, FN_LATENT_PREP, FN_HEAD_PRODUCT, FN_GATED_ACT, FN_BIAS_ADD, FN_ATTENTION_LATENT, FN_HEAD_PRODUCT_MMA,
     FN_EMBED_POS, FN_ATTN_PREP, FN_ATTENTION_PLAIN_WIDE, FN_ROUTE, FN_EXPERTS_ROWWISE, FN_ACTIVATION, FN_ADD2_RMSNORM,
-    FN_MOE_SORT, FN_MOE_GATHER, FN_MOE_COMBINE, FN_GEMM_GROUPED, FN_COUNT
+    FN_MOE_SORT, FN_MOE_GATHER, FN_MOE_COMBINE, FN_GEMM_GROUPED, FN_ATTENTION_PLAIN_MASKED, FN_COUNT
 };
 
 struct ExecProgram {

@@ -1,5 +1,5 @@
 """Importing this package registers every architecture the engine knows."""
-from . import lfm2, padadra, tufadra, vezalorn  # noqa: F401
+from . import bozovik, lfm2, padadra, tufadra, vezalorn  # noqa: F401
 from .decoder import DecoderModel
 
 __all__ = ["DecoderModel", "load_model"]

@@ -31,7 +31,7 @@ _SIGNATURES = {
         "cellm_gated_norm_add": [P, P, P, P, L, I, P, P, I, P, I, I, I, F, I, P],
         "cellm_stream_cast": [P, P, L, I, P],
         "cellm_mingru_scan": [P, P, L, I, P, P, I, P, L, P, P, I, I, I, I, I, I, P, P],
-        "cellm_latent_prep": [P, P, P, L, I, P, I, F, P, P, P, I, P, I, I, I, I, I, I, I, I, P, I, P, P],
+        "cellm_latent_prep": [P, P, P, L, I, P, I, F, P, P, P, I, P, I, I, I, I, I, I, I, I, I, P, I, P, P],
         "cellm_head_product": [P, L, L, P, L, L, P, I, I, I, I, I, P],
         "cellm_gated_act": [P, P, L, P, P, I, I, I, I, I, I, P],
         "cellm_bias_add": [P, P, P, I, I, I, I, P],
@@ -52,12 +52,22 @@ _SIGNATURES = {
         "cellm_scaled_add2": [P, P, P, F, L, I, P],
         "cellm_pair_norm_mean": [P, P, P, P, P, I, I, F, I, P],
         "cellm_conv_state_update": [P, L, I, P, P, P, L, I, P, I, I, I, P, P],
-        "cellm_sink_attn_prep": [P, P, P, P, L, I, P, P, I, P, L, I, P, P, F, P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P],
+        "cellm_sink_attn_prep": [P, P, P, P, L, I, P, P, I, P, L, I, P, P, F, P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, P, I, P, P],
+        "cellm_attention_plain_masked": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, P, F, I, P, L, I, P, P],
         "cellm_attention_plain_sink": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P, I, I, P, P],
         "cellm_hgrn2_scan": [P, P, L, I, P, L, I, I, I, P, P, P, P, I, I, I, I, I, P, P],
         "cellm_delta_prep": [P, P, P, P, P, L, I, I, P, I, P, L, I, P, L, P, P, P, P, P, I, I, I, I, I, F, P, P],
         "cellm_delta_scan": [P, P, L, I, P, P, P, P, P, P, I, I, I, I, I, P, P],
-        "cellm_head_norm_gate": [P, P, P, P, L, I, I, I, F, I, P],
+        "cellm_head_norm_gate": [P, P, P, P, L, I, I, I, F, I, I, P],
+        "cellm_gdelta_prep": [P, P, L, I, I, P, L, P, P, F, F, I, I, I, P],
+        "cellm_gdelta_scan": [P, P, L, I, P, L, I, I, I, P, P, P, I, I, I, I, P, P],
+        "cellm_add_scaled_norm": [P, P, P, F, P, F, I, P, P, P, I, I, I, F, I, I, P],
+        "cellm_stream_add_rows": [P, P, I, P, I, F, P, I, I, P, P],
+        "cellm_token_gate_mul": [P, P, L, P, L, I, I, P, I, I, I, I, I, P, P],
+        "cellm_scaled_rms_add": [P, P, P, F, I, I, F, P],
+        "cellm_weighted_sum2": [P, P, F, P, F, L, I, P],
+        "cellm_xielu": [P, P, L, I, I, P, I, P],
+        "cellm_head_gate_mul": [P, P, L, I, I, I, I, P],
     },
     "gemm_plain": {
         "cellm_gemm_plain": [P, P, P, I, I, I, L, L, L, I, I, P],

@@ -82,10 +82,12 @@ def conv_state_update(state: torch.Tensor, proj: torch.Tensor, col0: int, bias: 
 
 
 def sink_attn_prep(proj: torch.Tensor, col0: int, bias, taps, n_taps: int, conv_state, q_norm_w, k_norm_w, eps: float, qk_freq, rot: int,
-                   v_freq, interleaved: bool, ctx, cache, nh: int, nkv: int, hd: int, vd: int, act_dtype: torch.dtype) -> torch.Tensor:
+                   v_freq, interleaved: bool, ctx, cache, nh: int, nkv: int, hd: int, vd: int, act_dtype: torch.dtype,
+                   q_mult: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Bias, short convolution, norm over the projection, rotation of q, k (and v), and the write of k and v into the
-    token's page; returns q [T, nh * hd] in `act_dtype`. proj [T, ld] float32 holds q | k | v from column col0 on."""
-    _f32(proj, bias, taps, conv_state, q_norm_w, k_norm_w, qk_freq, v_freq)
+    token's page; returns q [T, nh * hd] in `act_dtype`. proj [T, ld] float32 holds q | k | v from column col0 on.
+    `q_mult` [nh]: a factor per query head."""
+    _f32(proj, bias, taps, conv_state, q_norm_w, k_norm_w, qk_freq, v_freq, q_mult)
     T = ctx.T
     q = torch.empty((T, nh * hd), dtype=act_dtype, device=proj.device)
     k, v, bt = cache.k, cache.v, cache.block_table
@@ -96,7 +98,7 @@ def sink_attn_prep(proj: torch.Tensor, col0: int, bias, taps, n_taps: int, conv_
         conv_state.stride(0) if conv_state is not None else 0, conv_state.shape[0] if conv_state is not None else 1 << 30,
         ptr(q_norm_w), ptr(k_norm_w), float(eps), ptr(qk_freq), int(rot), ptr(v_freq), int(interleaved), ptr(ctx.positions),
         ptr(ctx.seq_of_token), ptr(ctx.cu_seqlens), ptr(ctx.slot_ids), ptr(bt), bt.stride(0), k.shape[0], cache.page_size, T, nh, nkv, hd, vd,
-        tag(act_dtype), ptr(ctx.err), stream_of(proj)), "sink_attn_prep")
+        ptr(q_mult), tag(act_dtype), ptr(ctx.err), stream_of(proj)), "sink_attn_prep")
     return q
 
 
@@ -111,6 +113,26 @@ def attention_plain_sink(q: torch.Tensor, cache, ctx, nh: int, nkv: int, hd: int
                                                  bt.stride(0), k.shape[0], cache.page_size, q.shape[0], nh, nkv, hd, vd, float(scale),
                                                  int(window), ptr(sinks), ptr(unrot), int(interleaved), tag(q), ptr(ctx.err), stream_of(q)),
           "attention_plain_sink")
+    return out
+
+
+def attention_plain_masked(q: torch.Tensor, cache, ctx, nh: int, nkv: int, hd: int, vd: int, scale: float, window: int = 0,
+                           keep_first: int = 0, sinks: Optional[torch.Tensor] = None, fixed_sink: Optional[float] = None,
+                           gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The plain attention in its general form: position i sees key j <= i with i - j < window or j < keep_first (window 0:
+    every earlier key); `sinks` [nh] float32 (a learned sink per head) or `fixed_sink` (one sink score for all heads) is
+    one more term in the denominator; `gate` [T, >= nh] float32 (rows may be strided): head h's output times
+    sigmoid(gate[t, h]). A cache without a pool of values gives its key rows' first vd entries as values."""
+    _f32(sinks, gate)
+    k, bt = cache.k, cache.block_table
+    v = cache.v if cache.v is not None else k
+    out = torch.empty((q.shape[0], nh * vd), dtype=q.dtype, device=q.device)
+    check(fn(_LIB, "cellm_attention_plain_masked")(ptr(out), ptr(q), ptr(k), ptr(v), ptr(ctx.positions), ptr(ctx.seq_of_token), ptr(bt),
+                                                   bt.stride(0), k.shape[0], cache.page_size, q.shape[0], nh, nkv, hd, vd, v.shape[-1],
+                                                   float(scale), int(window), int(keep_first), ptr(sinks),
+                                                   float(fixed_sink) if fixed_sink is not None else 0.0, int(fixed_sink is not None),
+                                                   ptr(gate), gate.stride(0) if gate is not None else 0, tag(q), ptr(ctx.err), stream_of(q)),
+          "attention_plain_masked")
     return out
 
 
@@ -187,22 +209,52 @@ def delta_scan(qk, v, beta, decay, state: torch.Tensor, ctx, heads: int, kvh: in
     return o
 
 
+def gdelta_prep(proj: torch.Tensor, col_k: int, col_a: int, w_pre: torch.Tensor, w0: torch.Tensor, a_bias: torch.Tensor, rate: float,
+                unit_eps: float, heads: int, dim: int) -> torch.Tensor:
+    """Inputs of the generalized delta rule's walk, float32 [T, 3, heads * dim]: the decay exp(-rate * sigmoid(w_pre + w0)),
+    the unit key k / sqrt(sum(k^2) + unit_eps) of each head, and sigmoid(a_pre + a_bias) times the unit key. proj [T, ld]
+    float32 holds k at column col_k and a_pre at col_a; w_pre [T, heads * dim] float32 (rows may be strided)."""
+    _f32(proj, w_pre, w0, a_bias)
+    T = proj.shape[0]
+    vecs = torch.empty((T, 3, heads * dim), dtype=torch.float32, device=proj.device)
+    check(fn(_LIB, "cellm_gdelta_prep")(ptr(vecs), ptr(proj), proj.stride(0), int(col_k), int(col_a), ptr(w_pre), w_pre.stride(0), ptr(w0),
+                                        ptr(a_bias), float(rate), float(unit_eps), T, heads, dim, stream_of(proj)), "gdelta_prep")
+    return vecs
+
+
+def gdelta_scan(proj: torch.Tensor, col_r: int, col_k: int, col_v: int, vecs: torch.Tensor, state: torch.Tensor, ctx, heads: int,
+                dim: int, vd: int) -> torch.Tensor:
+    """The generalized delta rule S <- diag(d) S - (a u)(u^T S) + k v^T over every request's tokens of the step (both
+    terms read the old S); state [slots, heads, dim, vd] float32 is moved on. Returns S^T r per token and head, float32
+    [T, heads * vd]."""
+    _f32(proj, vecs, state)
+    o = torch.empty((ctx.T, heads * vd), dtype=torch.float32, device=proj.device)
+    check(fn(_LIB, "cellm_gdelta_scan")(ptr(o), ptr(state), state.stride(0), state.shape[0], ptr(proj), proj.stride(0), int(col_r), int(col_k),
+                                        int(col_v), ptr(vecs), ptr(ctx.cu_seqlens), ptr(ctx.slot_ids), ctx.B, heads, dim, vd, ptr(ctx.err),
+                                        stream_of(proj)), "gdelta_scan")
+    return o
+
+
 def head_norm_gate(o: torch.Tensor, w: torch.Tensor, gate: Optional[torch.Tensor], heads: int, vd: int, eps: float,
                    act_dtype: torch.dtype) -> torch.Tensor:
-    """o [T, heads * vd] float32 -> o / rms over each head * w [vd] (* sigmoid(gate [T, heads * vd], rows may be strided))."""
+    """o [T, heads * vd] float32 -> o / rms over each head * w (* sigmoid(gate [T, heads * vd], rows may be strided));
+    w [vd] serves every head, w [heads * vd] gives each head a row of its own."""
     _f32(o, w, gate)
     T = o.shape[0]
+    if w.numel() not in (vd, heads * vd):
+        raise ValueError("head_norm_gate: a weight of vd or of heads * vd values")
+    per_head = int(w.numel() != vd)
     out = torch.empty((T, heads * vd), dtype=act_dtype, device=o.device)
     check(fn(_LIB, "cellm_head_norm_gate")(ptr(out), ptr(o), ptr(w), ptr(gate), gate.stride(0) if gate is not None else 0, T, heads, vd,
-                                           float(eps), tag(act_dtype), stream_of(o)), "head_norm_gate")
+                                           float(eps), per_head, tag(act_dtype), stream_of(o)), "head_norm_gate")
     return out
 
 
 def activation(u: torch.Tensor, act: str, act_dtype: torch.dtype) -> torch.Tensor:
-    """act(u) for float32 u [T, n] (rows may be strided) in `act_dtype`; act: gelu, gelu_tanh, silu, relu, relu2."""
+    """act(u) for float32 u [T, n] (rows may be strided) in `act_dtype`; act: gelu, gelu_tanh, silu, relu, relu2, tanh."""
     _f32(u)
     T, n = u.shape
     h = torch.empty((T, n), dtype=act_dtype, device=u.device)
-    check(fn(_LIB, "cellm_activation")(ptr(h), ptr(u), u.stride(0), T, n, {"gelu": 0, "gelu_tanh": 1, "silu": 2, "relu": 3, "relu2": 4}[act],
+    check(fn(_LIB, "cellm_activation")(ptr(h), ptr(u), u.stride(0), T, n, {"gelu": 0, "gelu_tanh": 1, "silu": 2, "relu": 3, "relu2": 4, "tanh": 5}[act],
                                        tag(act_dtype), stream_of(u)), "activation")
     return h

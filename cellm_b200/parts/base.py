@@ -41,6 +41,7 @@ class TensorSpec:
 class PagedKV:
     """Keys and values that grow with the sequence, kept in pages.
     window = 0: all keys are kept; window = w: a token reads its last w keys.
+    keep_first = n (with a window): the sequence's first n keys stay readable too, so their pages are never given back.
     values = False: the rows serve as keys and values at once (a compressed cache whose values are a part
     of the key rows): only the pool of keys exists.
     value_dim = 0: value rows are as wide as key rows; otherwise the pool of values has rows of this width."""
@@ -49,6 +50,7 @@ class PagedKV:
     window: int = 0
     values: bool = True
     value_dim: int = 0
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)

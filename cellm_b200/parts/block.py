@@ -183,3 +183,97 @@ class GatedPostNormBlock(Block):
 
 
 register_block("gated_post_norm", GatedPostNormBlock)
+
+
+class ScaledPreNormBlock(Block):
+    """A pre-norm layer whose results join the 32-bit stream times a constant m, with two optional additions:
+
+        [at the start of a pass over looped layers:  x += the embedding row once more (passes after the first);  x += step[t]]
+        x += m * mixer(norm1(x));    x += m * feed_forward(norm2(x))        (the layer may have no feed-forward)
+        [x += m * rms_norm(P (act(G x) * e)) * w:  e is the layer's own part of a second embedding row of the token]
+
+    The norms may be layer norms or RMS norms (parts with `add_and_norm`): a sublayer's result is added and the next norm
+    formed by one kernel. The token's own row is gated by the stream itself (not normed), in the activations' type.
+
+    params: hidden_size, residual_mult (default 1);
+      token_rows (optional): {dim, offset, eps, activation}: columns offset .. offset + dim of the second table;
+      passes (optional): {order item: pass number} for the items at which this layer starts a pass, and
+      embedding_scale (the factor of the embedding row that is added again).
+    weights: token_table [vocab, >= offset + dim], token_gate [dim, H], token_proj [H, dim], token_norm [H] with token_rows;
+      pass_steps [passes, H] and embedding [vocab, H] with passes."""
+    graph_safe = True
+
+    @classmethod
+    def weight_specs(cls, params):
+        from .base import TensorSpec
+        H = int(params["hidden_size"])
+        specs = {}
+        tr = params.get("token_rows")
+        if tr:
+            specs["token_table"] = TensorSpec((int(tr["vocab"]), int(tr["table_width"])), "embedding")
+            specs["token_gate"] = TensorSpec((int(tr["dim"]), H), "linear")
+            specs["token_proj"] = TensorSpec((H, int(tr["dim"])), "linear")
+            specs["token_norm"] = TensorSpec((H,), "norm")
+        if params.get("passes"):
+            specs["pass_steps"] = TensorSpec((int(params["n_passes"]), H), "bias")
+            specs["embedding"] = TensorSpec((int(params["vocab"]), H), "embedding")
+        return specs
+
+    def __init__(self, mixer_norm, mixer, feed_forward_norm, feed_forward, params=None, weights=None, dtype=None):
+        import torch
+        from ..config.errors import ConfigError
+        from .linear import Linear
+        params, weights = params or {}, weights or {}
+        self.mixer_norm, self.mixer = mixer_norm, mixer
+        self.feed_forward_norm, self.feed_forward = feed_forward_norm, feed_forward
+        self.H, self.mult, self.dtype = int(params["hidden_size"]), float(params.get("residual_mult", 1.0)), dtype
+        if (feed_forward is None) != (feed_forward_norm is None):
+            raise ConfigError("pre_norm_scaled: a feed-forward and its norm come together")
+        for n in (mixer_norm, feed_forward_norm):
+            if n is not None and not hasattr(n, "add_and_norm"):
+                raise ConfigError("pre_norm_scaled: the norms must take an addend times a constant (layer_norm, rms_norm)")
+        self.token_rows = params.get("token_rows")
+        if self.token_rows:
+            tr = self.token_rows
+            self.token_table = weights["token_table"].contiguous()
+            self.token_gate, self.token_proj = Linear(weights["token_gate"], dtype), Linear(weights["token_proj"], dtype)
+            self.token_norm = weights["token_norm"].to(torch.float32).contiguous()
+            self.token_offset, self.token_dim = int(tr["offset"]), int(tr["dim"])
+            self.token_eps, self.token_act = float(tr["eps"]), tr.get("activation", "gelu_tanh")
+            if self.token_offset + self.token_dim > self.token_table.shape[1]:
+                raise ConfigError("pre_norm_scaled: the layer's part lies outside the token table's rows")
+        self.passes = {int(k): int(v) for k, v in (params.get("passes") or {}).items()}
+        if self.passes:
+            self.pass_steps = weights["pass_steps"].to(torch.float32).contiguous()
+            self.embedding = weights["embedding"].contiguous()
+            self.embedding_scale = float(params.get("embedding_scale", 1.0))
+            if max(self.passes.values()) >= self.pass_steps.shape[0]:
+                raise ConfigError("pre_norm_scaled: more passes than step vectors")
+
+    def forward(self, residual: Residual, ctx: StepContext, cache: CacheBinding) -> None:
+        from .. import ops
+        x = residual.flush()
+        if self.passes:
+            t = self.passes.get(ctx.extras.get("order_item"))
+            if t is not None:
+                ops.stream_add_rows(x, self.embedding if t > 0 else None, ctx.token_ids, self.embedding_scale, self.pass_steps[t], ctx.err)
+        m = self.mult
+        a = self.mixer.forward(self.mixer_norm.add_and_norm(x, None, 0.0), ctx, cache)
+        if self.feed_forward is not None:
+            a = self.feed_forward.forward(self.feed_forward_norm.add_and_norm(x, a.contiguous(), m), ctx)
+        if not self.token_rows:
+            ops.add_scaled_norm(x, a.contiguous(), m, None, 0.0, "none", None, None, 0.0, self.dtype, want=False)
+            return
+        # x += m * a, and the sum in the activations' type for the gate's product
+        xb = ops.add_scaled_norm(x, a.contiguous(), m, None, 0.0, "none", None, None, 0.0, self.dtype)
+        g = self.token_gate(xb, out_dtype=torch_float32())
+        e = ops.token_gate_mul(g, self.token_table, self.token_offset, ctx.token_ids, self.token_act, self.dtype, ctx.err)
+        ops.scaled_rms_add(x, self.token_proj(e, out_dtype=torch_float32()), self.token_norm, m, self.token_eps)
+
+
+def torch_float32():
+    import torch
+    return torch.float32
+
+
+register_block("pre_norm_scaled", ScaledPreNormBlock)

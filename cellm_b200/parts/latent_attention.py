@@ -8,7 +8,10 @@ row is cached.
 Since q_h . (K_h c) = (K_h^T q_h) . c, the attention runs over the cached rows themselves with one key/value "head":
 the query of head h becomes [K_h^T q_h | rotated part], the weighted sum of the rows' first kv_rank values is formed,
 and V_h turns it into the head's output. The rotation is a position part of its own (`position`), applied to the last
-rot_dim values of each query head and to the shared key part."""
+rot_dim values of each query head and to the shared key part, in pairs that lie side by side or half a rotation apart.
+Optional: a sliding window (position i sees the rows j with 0 <= i - j < window; rows that no later token can read give
+their pages back) and a learned sink per head (one more term exp(sink_h) in the softmax's denominator, with no key and
+no value)."""
 from __future__ import annotations
 
 import torch
@@ -24,20 +27,24 @@ class LatentAttentionMixer(Mixer):
     graph_safe = True
 
     """params: hidden_size, heads, dim, rot_dim, vdim, kv_rank, scale, eps (of the latent's norm),
-    position (PartSpec of a rotation over rot_dim values, or None).
+    position (PartSpec of a rotation over rot_dim values, or None), window (default 0: every earlier row), sinks (default
+    False), out_dtype32 (default False).
     weights: q [heads*(dim+rot_dim), H], dkv [kv_rank+rot_dim, H], dkv_norm [kv_rank], uk [heads*dim, kv_rank],
-    uv [heads*vdim, kv_rank], o [H, heads*vdim]."""
+    uv [heads*vdim, kv_rank], o [H, heads*vdim]; sinks [heads]."""
 
     @classmethod
     def weight_specs(cls, params):
         H, nh, d, r, vd, rank = (params[k] for k in ("hidden_size", "heads", "dim", "rot_dim", "vdim", "kv_rank"))
-        return {"q": TensorSpec((nh * (d + r), H), "linear"), "dkv": TensorSpec((rank + r, H), "linear"),
-                "dkv_norm": TensorSpec((rank,), "norm"), "uk": TensorSpec((nh * d, rank), "linear"),
-                "uv": TensorSpec((nh * vd, rank), "linear"), "o": TensorSpec((H, nh * vd), "linear")}
+        specs = {"q": TensorSpec((nh * (d + r), H), "linear"), "dkv": TensorSpec((rank + r, H), "linear"),
+                 "dkv_norm": TensorSpec((rank,), "norm"), "uk": TensorSpec((nh * d, rank), "linear"),
+                 "uv": TensorSpec((nh * vd, rank), "linear"), "o": TensorSpec((H, nh * vd), "linear")}
+        if params.get("sinks"):
+            specs["sinks"] = TensorSpec((nh,), "sink")
+        return specs
 
     @classmethod
     def cache_need(cls, params):
-        return PagedKV(1, int(params["kv_rank"]) + int(params["rot_dim"]), 0, values=False)
+        return PagedKV(1, int(params["kv_rank"]) + int(params["rot_dim"]), int(params.get("window") or 0), values=False)
 
     def __init__(self, params: dict, weights: dict, dtype: torch.dtype):
         self.H, self.dtype = int(params["hidden_size"]), dtype
@@ -53,10 +60,11 @@ class LatentAttentionMixer(Mixer):
         pos: PartSpec | None = params.get("position")
         self.position = part_class("position", pos.kind)(pos.params, self.c_norm_w.device) if pos is not None else None
         rot = self.position.rotation() if self.position is not None else (0, True, None)
-        if rot is None or (rot[0] and not rot[1]) or rot[0] > self.r:
-            raise ConfigError("latent_attention: the position encoding must be a rotation of interleaved pairs "
-                              "over at most rot_dim values")
-        self.rot, self.inv_freq = int(rot[0]), rot[2]
+        if rot is None or rot[0] > self.r:
+            raise ConfigError("latent_attention: the position encoding must be a rotation over at most rot_dim values")
+        self.rot, self.interleaved, self.inv_freq = int(rot[0]), bool(rot[1]), rot[2]
+        self.window = int(params.get("window") or 0)
+        self.sinks = weights["sinks"].to(torch.float32).contiguous() if params.get("sinks") else None
         self.extra = 0
         self._record = None
 
@@ -81,7 +89,8 @@ class LatentAttentionMixer(Mixer):
             p.heads, p.dim, p.rot_dim, p.vdim, p.rank, p.scale = self.nh, self.d, self.r, self.vd, self.rank, self.scale
             p.c_norm_w, p.c_norm_dtype, p.eps = self.c_norm_w.data_ptr(), tag(self.c_norm_w), self.eps
             p.rot, p.inv_freq, p.extra = self.rot, R.ptr(self.inv_freq), self.extra
-            self._record = R.Record(R.LATENT_ATTENTION, p, keep=[self.inv_freq], part=self)
+            p.interleaved, p.window, p.sinks = int(self.interleaved), self.window, R.ptr(self.sinks)
+            self._record = R.Record(R.LATENT_ATTENTION, p, keep=[self.inv_freq, self.sinks], part=self)
         return self._record
 
     def emit(self, emitter) -> None:

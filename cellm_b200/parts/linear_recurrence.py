@@ -15,6 +15,17 @@
     out = W_o (rms_norm(o per head) * w * sigmoid(W_g2 (W_g1 h)))
     Value head h reads the q and k of head floor(h / (heads / qk_heads)).
 
+`general_delta`: the generalized delta rule, whose decay and removal both read the old state.
+
+    r, k, v = W h   (heads x dim each)
+    d = exp(-rate * sigmoid(W_w2 tanh(W_w1 h) + w0))    a decay per head and key channel (rate: a constant, exp(-1/2) by default)
+    a = sigmoid(W_a h + a_bias)                         a removal rate per head and key channel
+    u = k / sqrt(sum(k^2) + unit_eps)                   the unit key of each head
+    S <- diag(d) S - (a * u)(u^T S) + k v^T (the old S on the right);   o = S^T r
+    out = W_o (rms_norm(o per head) * w * sigmoid(W_g h))    (w: a row for every head)
+
+`weighted_pair`: two mixers side by side over the same input, out = a * first(h) + b * second(h) with constants a, b.
+
 Everything that enters a recurrence is 32-bit (the projections keep their 32-bit sums; gates, decays, unit vectors and
 the state are computed in 32-bit), and a request's tokens are walked in order from the state the step before left, so
 the state after a token does not depend on how the sequence was cut. The delta rule also keeps the convolution's last
@@ -146,6 +157,59 @@ class GatedDeltaMixer(Mixer):
 register_mixer("gated_delta", GatedDeltaMixer)
 
 
+class GeneralDeltaMixer(Mixer):
+    graph_safe = True
+
+    """params: hidden_size, heads, dim, eps, rate (default exp(-1/2)), unit_eps (default 1e-6), decay_rank (-1: whatever the
+    file's tensor has), out_dtype32 (default False).
+    weights: r, k, v, g, a [heads*dim, H]; a_bias [heads*dim]; w1 [decay_rank, H], w2 [heads*dim, decay_rank], w0 [heads*dim];
+    norm [heads*dim]; o [H, heads*dim]."""
+
+    @classmethod
+    def weight_specs(cls, params):
+        H, h, d = (int(params[k]) for k in ("hidden_size", "heads", "dim"))
+        rank = int(params.get("decay_rank", -1))
+        n = h * d
+        return {"r": TensorSpec((n, H), "linear"), "k": TensorSpec((n, H), "linear"), "v": TensorSpec((n, H), "linear"),
+                "g": TensorSpec((n, H), "linear"), "a": TensorSpec((n, H), "linear"), "a_bias": TensorSpec((n,), "bias"),
+                "w1": TensorSpec((rank, H), "linear"), "w2": TensorSpec((n, rank), "linear_wide"), "w0": TensorSpec((n,), "bias"),
+                "norm": TensorSpec((n,), "norm"), "o": TensorSpec((H, n), "linear")}
+
+    @classmethod
+    def cache_need(cls, params):
+        return FixedState((int(params["heads"]), int(params["dim"]), int(params["dim"])), torch.float32)
+
+    def __init__(self, params: dict, weights: dict, dtype: torch.dtype):
+        import math
+        self.H, self.heads, self.dim = (int(params[k]) for k in ("hidden_size", "heads", "dim"))
+        self.eps, self.unit_eps, self.dtype = float(params["eps"]), float(params.get("unit_eps", 1e-6)), dtype
+        self.rate = float(params.get("rate", math.exp(-0.5)))
+        if weights["w2"].shape[1] != weights["w1"].shape[0]:
+            raise ConfigError("general_delta: the two matrices of the decay's low-rank product do not fit each other")
+        self.rank = int(weights["w1"].shape[0])
+        # one product over the mixer's input: r | k | v | a | g | the decay's first matrix, as 32-bit sums
+        self.in_proj = Linear(stack_rows(weights["r"], weights["k"], weights["v"], weights["a"], weights["g"], weights["w1"]), dtype)
+        self.w2 = Linear(weights["w2"], dtype)
+        self.out_proj = Linear(weights["o"], dtype)
+        self.out32 = bool(params.get("out_dtype32", False))
+        self.a_bias, self.w0, self.norm_w = _f32(weights, "a_bias"), _f32(weights, "w0"), _f32(weights, "norm")
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
+        from .. import ops
+        state = bindings_of(cache, 1)[0].state
+        n = self.heads * self.dim
+        proj = self.in_proj(x, out_dtype=torch.float32)
+        low = ops.activation(proj[:, 5 * n:], "tanh", self.dtype)
+        w_pre = self.w2(low, out_dtype=torch.float32)
+        vecs = ops.gdelta_prep(proj, n, 3 * n, w_pre, self.w0, self.a_bias, self.rate, self.unit_eps, self.heads, self.dim)
+        o = ops.gdelta_scan(proj, 0, n, 2 * n, vecs, state, ctx, self.heads, self.dim, self.dim)
+        y = ops.head_norm_gate(o, self.norm_w, proj[:, 4 * n:5 * n], self.heads, self.dim, self.eps, self.dtype)
+        return self.out_proj(y, out_dtype=torch.float32 if self.out32 else None)
+
+
+register_mixer("general_delta", GeneralDeltaMixer)
+
+
 class SideBySideMixer(Mixer):
     graph_safe = True
 
@@ -210,3 +274,46 @@ class SideBySideMixer(Mixer):
 
 
 register_mixer("side_by_side", SideBySideMixer)
+
+
+class WeightedPairMixer(SideBySideMixer):
+    graph_safe = True
+
+    """Two mixers that read the same input; the result is first_scale * first(h) + second_scale * second(h), formed in
+    32-bit from the two mixers' 32-bit results and returned so. Both keep their own caches: the item's needs are the first
+    mixer's followed by the second's.
+
+    params: hidden_size, first, second (PartSpecs of registered mixers; their weights' names are prefixed `first.` and
+    `second.` here), first_scale, second_scale."""
+
+    @classmethod
+    def weight_specs(cls, params):
+        specs = {}
+        for name, spec, klass in cls._subs(params):
+            for local, ts in klass.weight_specs(spec.params).items():
+                specs[f"{name}.{local}"] = ts
+        return specs
+
+    def __init__(self, params: dict, weights: dict, dtype: torch.dtype):
+        self.H, self.dtype = int(params["hidden_size"]), dtype
+        self.scales = (float(params["first_scale"]), float(params["second_scale"]))
+        self.parts, self.counts = [], []
+        for name, spec, klass in self._subs(params):
+            own = {k[len(name) + 1:]: v for k, v in weights.items() if k.startswith(name + ".")}
+            sub_params = dict(spec.params)
+            sub_params.setdefault("out_dtype32", True)
+            self.parts.append(klass(sub_params, own, dtype))
+            n = klass.cache_need(spec.params)
+            self.counts.append(len(n) if isinstance(n, (tuple, list)) else (0 if n is None else 1))
+        self.first, self.second = self.parts
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
+        from .. import ops
+        a = self.first.forward(x, ctx, self._binding(cache, 0, self.counts[0]))
+        b = self.second.forward(x, ctx, self._binding(cache, self.counts[0], self.counts[1]))
+        if a.dtype != b.dtype:
+            a, b = a.to(torch.float32), b.to(torch.float32)
+        return ops.weighted_sum2(a.contiguous(), self.scales[0], b.contiguous(), self.scales[1])
+
+
+register_mixer("weighted_pair", WeightedPairMixer)

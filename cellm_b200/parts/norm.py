@@ -52,5 +52,46 @@ class RMSNorm(Norm):
             residual.pending = delta      # the stream itself was not updated
         return y
 
+    def add_and_norm(self, x: torch.Tensor, addend: Optional[torch.Tensor], mult: float) -> torch.Tensor:
+        """x += mult * addend (in place, 32-bit; None: nothing is added), then the norm of the sum."""
+        if self.groups != 1:
+            raise ConfigError("rms_norm: an addend times a constant is not taken by a norm in groups")
+        if getattr(self, "_w32", None) is None:
+            self._w32 = self.weight.to(torch.float32).contiguous()
+        return ops.add_scaled_norm(x, addend, mult, None, 0.0, "rms", self._w32, None, self.eps, self.dtype)
+
 
 register_norm("rms_norm", RMSNorm)
+
+
+class LayerNorm(Norm):
+    graph_safe = True
+
+    """(x - mean) / sqrt(var + eps) * w + b over the last axis, var the mean of the squared deviations; all of it 32-bit.
+    params: dim, eps, bias (default True). weights: weight [dim], bias [dim]."""
+
+    @classmethod
+    def weight_specs(cls, params):
+        specs = {"weight": TensorSpec((params["dim"],), "norm")}
+        if params.get("bias", True):
+            specs["bias"] = TensorSpec((params["dim"],), "bias")
+        return specs
+
+    def __init__(self, params: dict, weights: dict, dtype: torch.dtype):
+        self.dim, self.eps, self.dtype = int(params["dim"]), float(params["eps"]), dtype
+        self.weight = weights["weight"].to(torch.float32).contiguous()
+        self.bias = weights["bias"].to(torch.float32).contiguous() if params.get("bias", True) else None
+
+    def forward(self, residual: Residual, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        delta, residual.pending = residual.pending, None
+        y = ops.add_scaled_norm(residual.x, delta, 1.0, None, 0.0, "layer", self.weight, self.bias, self.eps, self.dtype, rows)
+        if rows is not None and delta is not None:
+            residual.pending = delta      # the stream itself was not updated
+        return y
+
+    def add_and_norm(self, x: torch.Tensor, addend: Optional[torch.Tensor], mult: float) -> torch.Tensor:
+        """x += mult * addend (in place, 32-bit; None: nothing is added), then the norm of the sum."""
+        return ops.add_scaled_norm(x, addend, mult, None, 0.0, "layer", self.weight, self.bias, self.eps, self.dtype)
+
+
+register_norm("layer_norm", LayerNorm)

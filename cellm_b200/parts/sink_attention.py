@@ -6,8 +6,12 @@
           possibly stretched by wavelength)
     v:    every value head turns over all its entries by its own position j, pair m by j * theta^(-2m/vd), and is
           cached so; a head's output at position i (the weighted sum of values) is turned back by -i * theta^(-2m/vd)
-    softmax over the keys j with 0 <= i - j < window (window 0: all earlier keys); the denominator also holds
-          exp(sink_h): a learned number per head with no key and no value, not scaled, counted once
+    softmax over the keys j with 0 <= i - j < window (window 0: all earlier keys; with `keep_first` n the sequence's
+          first n keys stay visible behind the window, at their true positions); the denominator also holds
+          exp(sink_h): a learned number per head with no key and no value, not scaled, counted once (or, with
+          `fixed_sink`, exp of one given score for every head: 0 adds one to the denominator)
+    scores of head h times a learned number per head (`head_temperature`, optional)
+    head h's output times sigmoid(G h)_h, one number per head from a product over the mixer's input (`head_gate`, optional)
     out = W_o (heads side by side)
 
 Scores, softmax, norms, angles and the convolutions' sums are 32-bit. The request keeps pages of keys and values
@@ -50,9 +54,11 @@ class SinkAttentionMixer(Mixer):
     """params: hidden_size, num_heads, num_kv_heads, head_dim, value_dim (default head_dim), scale, window (default 0),
     bias (default False: q, k, v have none), conv_taps (default 0: no convolution), qk_norm_eps (None: no norm over the
     projection), position (PartSpec of a rotation, or None), value_theta (None: values are not rotated),
-    sinks (default True), out_dtype32 (default False: out_proj's result in the activations' type).
+    sinks (default True), out_dtype32 (default False: out_proj's result in the activations' type), keep_first (default 0),
+    fixed_sink (None, or the sink's score where it is no learned number; not beside sinks), head_gate, head_temperature
+    (default False).
     weights: q_proj [nh*hd, H], k_proj [nkv*hd, H], v_proj [nkv*vd, H], out_proj [H, nh*vd]; q_bias, k_bias, v_bias;
-    q_conv [nh*hd, taps], k_conv, v_conv; q_norm [nh*hd], k_norm [nkv*hd]; sinks [nh]."""
+    q_conv [nh*hd, taps], k_conv, v_conv; q_norm [nh*hd], k_norm [nkv*hd]; sinks [nh]; gate [nh, H]; temperature [nh]."""
 
     @classmethod
     def _sizes(cls, params):
@@ -75,12 +81,17 @@ class SinkAttentionMixer(Mixer):
             specs.update(q_norm=TensorSpec((nh * hd,), "norm"), k_norm=TensorSpec((nkv * hd,), "norm"))
         if params.get("sinks", True):
             specs["sinks"] = TensorSpec((nh,), "sink")
+        if params.get("head_gate"):
+            specs["gate"] = TensorSpec((nh, H), "linear")
+        if params.get("head_temperature"):
+            specs["temperature"] = TensorSpec((nh,), "norm")
         return specs
 
     @classmethod
     def cache_need(cls, params):
         nh, nkv, hd, vd = cls._sizes(params)
-        paged = PagedKV(nkv, hd, int(params.get("window") or 0), value_dim=vd if vd != hd else 0)
+        window = int(params.get("window") or 0)
+        paged = PagedKV(nkv, hd, window, value_dim=vd if vd != hd else 0, keep_first=int(params.get("keep_first") or 0) if window else 0)
         taps = int(params.get("conv_taps") or 0)
         if taps > 1:
             return (paged, FixedState((taps - 1, nh * hd + nkv * hd + nkv * vd), torch.float32))
@@ -95,7 +106,15 @@ class SinkAttentionMixer(Mixer):
         self.taps = int(params.get("conv_taps") or 0)
         self.dtype = dtype
         f32 = lambda *names: torch.cat([weights[n].to(torch.float32).reshape(-1) for n in names]).contiguous()
-        self.qkv = Linear(stack_rows(weights["q_proj"], weights["k_proj"], weights["v_proj"]), dtype)
+        self.keep_first = int(params.get("keep_first") or 0) if self.window else 0
+        self.fixed_sink = params.get("fixed_sink")
+        if self.fixed_sink is not None and params.get("sinks", True):
+            raise ConfigError("sink_attention: a fixed sink beside learned ones")
+        # the gate's rows ride behind q | k | v: one product over the mixer's input forms all of them as 32-bit sums
+        mats = [weights["q_proj"], weights["k_proj"], weights["v_proj"]] + ([weights["gate"]] if params.get("head_gate") else [])
+        self.gated = bool(params.get("head_gate"))
+        self.temperature = f32("temperature") if params.get("head_temperature") else None
+        self.qkv = Linear(stack_rows(*mats), dtype)
         self.out_proj = Linear(weights["out_proj"], dtype)
         self.out32 = bool(params.get("out_dtype32", False))
         self.bias = f32("q_bias", "k_bias", "v_bias") if params.get("bias") else None
@@ -131,12 +150,26 @@ class SinkAttentionMixer(Mixer):
         proj = self.qkv(x, out_dtype=torch.float32)
         q = ops.sink_attn_prep(proj, 0, self.bias, self.conv_w, self.taps, conv_state, self.q_norm_w, self.k_norm_w,
                                float(self.eps or 0.0), self.qk_freq, self.rot, self.v_freq, self.interleaved, ctx, pages,
-                               self.nh, self.nkv, self.hd, self.vd, self.dtype)
+                               self.nh, self.nkv, self.hd, self.vd, self.dtype, self.temperature)
         if conv_state is not None:
             ops.conv_state_update(conv_state, proj, 0, self.bias, self.taps, ctx)
-        if self.dtype == torch.bfloat16 and self.hd == self.vd and self.hd in (32, 64, 128) and OPTIONS["tensor_cores"]:
-            o = ops.attention_flash_sink(q, pages, ctx, self.nh, self.nkv, self.hd, self.scale, self.window, self.sinks,
+        gate = proj[:, proj.shape[1] - self.nh:] if self.gated else None
+        tc = self.dtype == torch.bfloat16 and self.hd == self.vd and self.hd in (32, 64, 128) and OPTIONS["tensor_cores"]
+        if tc and not self.keep_first:
+            sinks = self.sinks
+            if self.fixed_sink is not None:
+                if getattr(self, "_fixed", None) is None:
+                    self._fixed = torch.full((self.nh,), float(self.fixed_sink), dtype=torch.float32, device=q.device)
+                sinks = self._fixed
+            o = ops.attention_flash_sink(q, pages, ctx, self.nh, self.nkv, self.hd, self.scale, self.window, sinks,
                                          self.v_freq, self.interleaved)
+            if gate is not None:
+                ops.head_gate_mul(o, gate, self.nh)
+        elif self.keep_first or self.fixed_sink is not None or gate is not None:
+            if self.v_freq is not None:
+                raise ConfigError("sink_attention: rotated values beside kept first keys, a fixed sink or a gate per head")
+            o = ops.attention_plain_masked(q, pages, ctx, self.nh, self.nkv, self.hd, self.vd, self.scale, self.window, self.keep_first,
+                                           self.sinks, self.fixed_sink, gate)
         else:
             o = ops.attention_plain_sink(q, pages, ctx, self.nh, self.nkv, self.hd, self.vd, self.scale, self.window, self.sinks,
                                          self.v_freq, self.interleaved)

@@ -340,6 +340,7 @@ class Program:
                     y = part.forward(res, rows=rows if regs.phase == 2 else None)
                     regs.y = self._own(y, (n_y, H))
                 else:
+                    ctx.extras["order_item"] = int(regs.item)       # a layer that runs more than once may ask which run this is
                     part.forward(res, ctx, bindings[regs.item])
                     regs.y = None
                 if res.x is not x:

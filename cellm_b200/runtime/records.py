@@ -82,7 +82,8 @@ class MinGruParams(Structure):
 class LatentAttentionParams(Structure):
     _fields_ = [("in_proj", ExecLinear), ("out_proj", ExecLinear), ("absorb_k", PTR), ("expand_v", PTR),
                 ("heads", I64), ("dim", I64), ("rot_dim", I64), ("vdim", I64), ("rank", I64), ("scale", F64),
-                ("c_norm_w", PTR), ("c_norm_dtype", I64), ("eps", F64), ("rot", I64), ("inv_freq", PTR), ("extra", I64)]
+                ("c_norm_w", PTR), ("c_norm_dtype", I64), ("eps", F64), ("rot", I64), ("inv_freq", PTR), ("extra", I64),
+                ("interleaved", I64), ("window", I64), ("sinks", PTR)]
 
 
 class GatedMlpParams(Structure):
@@ -121,7 +122,8 @@ ENTRY_POINTS = [("kernels_common", "cellm_embed"), ("kernels_common", "cellm_add
                 ("kernels_common", "cellm_attention_plain_wide"), ("kernels_common", "cellm_route"),
                 ("kernels_common", "cellm_experts_rowwise"), ("kernels_common", "cellm_activation"),
                 ("kernels_common", "cellm_add2_rmsnorm"), ("kernels_common", "cellm_moe_sort"), ("kernels_common", "cellm_moe_gather"),
-                ("kernels_common", "cellm_moe_combine"), ("gemm_tcgen05", "cellm_gemm_grouped_tcgen05")]
+                ("kernels_common", "cellm_moe_combine"), ("gemm_tcgen05", "cellm_gemm_grouped_tcgen05"),
+                ("kernels_common", "cellm_attention_plain_masked")]
 # libraries a model whose activations are 32-bit never calls into (they need not be compiled for it)
 BF16_ONLY_LIBRARIES = ("attention_decode", "attention_tc", "attention_flash", "gemm_tcgen05", "attention_latent")
 # libraries that only records of these kinds reach (a program without such a record need not have them compiled)
