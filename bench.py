@@ -274,12 +274,14 @@ def step_matrices(model, tokens: int):
 
 def design_shapes(design: str) -> dict:
     from cellm_b200.config import presets
-    return {"vezalorn": presets.VEZALORN_SHAPES, "tufadra": presets.TUFADRA_SHAPES, "padadra": presets.PADADRA_SHAPES}[design]
+    return {"vezalorn": presets.VEZALORN_SHAPES, "tufadra": presets.TUFADRA_SHAPES, "padadra": presets.PADADRA_SHAPES,
+            "bozovik": presets.BOZOVIK_SHAPES}[design]
 
 
 def compare_designs(args, rng) -> int:
     """Prefill (one 2,048-token prompt) and decode (batch 8 and 1 after 2,048-token prompts) of the new design and of
-    LFM2 at equal sizes, device-timed with CUDA events through the step function."""
+    the model beside it (LFM2, or the closest other design) at equal sizes, device-timed with CUDA events through the
+    step function."""
     import torch
     from cellm_b200 import write_random_model
     from cellm_b200.config.presets import LFM2_SHAPES
@@ -290,7 +292,8 @@ def compare_designs(args, rng) -> int:
     for size in [s for s in args.sizes.split(",") if s]:
         shape, like = design_shapes(args.design)[size]
         row = {}
-        for name, config in ((args.design, shape), (like, LFM2_SHAPES[like])):
+        beside = (like, LFM2_SHAPES[like]) if isinstance(like, str) else like
+        for name, config in ((args.design, shape), beside):
             with tempfile.TemporaryDirectory(prefix="cellm_bench_") as d:
                 write_random_model(d, config, seed=0, dtype="bfloat16", init=InitSpec(norm_jitter=0.0))
                 loaded = load_model(d, "bfloat16", "cuda:0")
@@ -315,7 +318,7 @@ def compare_designs(args, rng) -> int:
             del loaded
             torch.cuda.empty_cache()
         out[size] = row
-    print(json.dumps({"metric": "prefill and decode of %s beside LFM2 at equal sizes" % args.design, "dtype": "bf16",
+    print(json.dumps({"metric": "prefill and decode of %s beside %s at equal sizes" % (args.design, "LFM2" if isinstance(like, str) else like[0]), "dtype": "bf16",
                       "data": "synthetic: random token ids, random-init weights", "peaks": pk_src, "steps": args.steps,
                       "warmup": args.warmup, "prompt_len": PROMPT_LEN, "sizes": out}))
     return 0
@@ -329,7 +332,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 runs")
-    ap.add_argument("--design", default=None, choices=["vezalorn", "tufadra", "padadra"],
+    ap.add_argument("--design", default=None, choices=["vezalorn", "tufadra", "padadra", "bozovik"],
                     help="instead of the default workload: prefill and decode throughput of this design at a few sizes, "
                          "beside LFM2 at equal width, depth and feed-forward (random weights); prints one JSON line")
     ap.add_argument("--sizes", default="700m,1.2b", help="with --design: which of the shapes to run")

@@ -97,3 +97,36 @@ PADADRA_SHAPES = {
     "1.2b": (_padadra(2048, 16, [2, 5, 8, 10, 12, 14], 32, 8, 16, 8192), "lfm2-1.2b"),
     "700m": (_padadra(1536, 16, [2, 5, 8, 10, 12, 14], 24, 8, 12, 6912), "lfm2-700m"),
 }
+
+
+# ---- Bozovik shapes beside Padadra's -------------------------------------------------------------------------------
+def _bozovik(width: int, layers: int, parallel_at, attention_at, heads: int, kv_heads: int, rec_heads: int, latent_heads: int, ff: int,
+             vocab: int = 65536) -> dict:
+    """Layers of a width and count that a Padadra shape has: the windowed attention that keeps its first keys beside the
+    generalized delta rule (states of 64 x 64 a head) where Padadra has its two mixers side by side, attention over every
+    earlier key at a few places, latent attention (heads of 128 + 64, a latent of 512, a window of 1,024) elsewhere, a
+    feed-forward of Padadra's width behind every mixer and a side input of 64 values a layer. No layers are looped, so
+    that both models do a layer's work as often."""
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 64, "scale": 0.125, "mask": {"size": 1024, "keep_first": 64},
+            "rot": {"base": 1000000.0, "dims": 64}}
+    right = {"heads": rec_heads, "dim": 64, "decay_rank": 64}
+    full = {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 64, "scale": 0.125, "rot": {"base": 1000000.0, "dims": 32}}
+    lat = {"heads": latent_heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5, "mask": {"size": 1024},
+           "rot": {"base": 500000.0, "dims": 64}}
+    mlp = {"kind": "dense", "ff": ff}
+
+    def layer(i):
+        if i in parallel_at:
+            return {"type": "parallel", "mixer": {"left": dict(left), "right": dict(right), "left_scale": 0.6, "right_scale": 0.5}, "mlp": dict(mlp)}
+        if i in attention_at:
+            return {"type": "attention", "mixer": dict(full), "mlp": dict(mlp)}
+        return {"type": "latent_attention", "mixer": dict(lat), "mlp": dict(mlp)}
+    return {"architecture": "Bozovik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+            "embedding": {"scale": 1.0}, "token_side": {"dim": 64}, "layers": [layer(i) for i in range(layers)]}
+
+
+# name -> (Bozovik shape, (the closest design's name, its shape of equal width, depth and feed-forward))
+BOZOVIK_SHAPES = {
+    "1.2b": (_bozovik(2048, 16, [2, 5, 8, 10, 12, 14], [0, 7, 15], 32, 8, 32, 16, 8192), ("padadra", PADADRA_SHAPES["1.2b"][0])),
+    "700m": (_bozovik(1536, 16, [2, 5, 8, 10, 12, 14], [0, 7, 15], 24, 8, 24, 12, 6912), ("padadra", PADADRA_SHAPES["700m"][0])),
+}

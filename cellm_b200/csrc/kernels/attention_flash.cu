@@ -27,6 +27,18 @@
 
 namespace {
 
+// What the general form adds to a row: the sequence's first `keep_first` keys stay visible behind the window, and a head's
+// output is multiplied by the sigmoid of one number per (token, head) (`gate` [T, gate_ld] 32-bit; null: none).
+struct FlashExtras {
+    int keep_first = 0;
+    const float* gate = nullptr;
+    long long gate_ld = 0;
+};
+
+__device__ __forceinline__ float gate_factor(const FlashExtras& ex, int token, int head) {
+    return ex.gate ? 1.f / (1.f + __expf(-ex.gate[(size_t)token * ex.gate_ld + head])) : 1.f;
+}
+
 template <int HD, int NWARPS>
 __global__ void __launch_bounds__(NWARPS * 32, (HD <= 64 && NWARPS == 4) ? 4 : 1)
 attention_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
@@ -35,7 +47,7 @@ attention_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part
                        const int* __restrict__ ctx_lens, const int* __restrict__ block_table, int bt_stride,
                        int B, int T, int num_pages, int page_size, int nh, int nkv, float scale_log2e, int window,
                        const float* __restrict__ sinks, const float* __restrict__ unrot, int interleaved,
-                       int* __restrict__ err) {
+                       const FlashExtras ex, int* __restrict__ err) {
     constexpr int BM = 16 * NWARPS, BN = FA_BN, CH = HD / 8, NT = HD / 8, THREADS = NWARPS * 32;
     extern __shared__ __align__(128) uint8_t fa_smem[];
     uint8_t* q_s = fa_smem;                              // [BM][HD]
@@ -64,8 +76,14 @@ attention_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part
     const int key_end = ctx + t_hi + 1;
     const int key_begin = window > 0 ? max(0, ctx + t_lo - window + 1) : 0;
     const int kb_begin = key_begin / BN, kb_end = (key_end + BN - 1) / BN;
-    const int per = (kb_end - kb_begin + nsplit - 1) / nsplit;
-    const int my_begin = kb_begin + split * per, my_end = min(kb_end, my_begin + per);
+    // the blocks this tile walks: those that hold kept first keys and lie wholly before the window's first block, then
+    // the window's; a CTA's piece is a run of this list
+    const int keep_first = ex.keep_first;
+    const int kf_blocks = keep_first > 0 ? min((min(keep_first, key_end) + BN - 1) / BN, kb_begin) : 0;
+    const int n_blocks = kf_blocks + kb_end - kb_begin;
+    const int per = (n_blocks + nsplit - 1) / nsplit;
+    const int my_begin = split * per, my_end = min(n_blocks, my_begin + per);
+    auto block_of = [&](int i) { return i < kf_blocks ? i : kb_begin + (i - kf_blocks); };
     const int* bt = block_table + (size_t)b * bt_stride;
     const size_t page_elems = (size_t)nkv * page_size * HD;
     const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;   // -1: not a power of two
@@ -89,7 +107,7 @@ attention_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part
 #pragma unroll
         for (int it = 0; it < KV_ITERS; ++it) {
             const int i = threadIdx.x + it * THREADS, j = kb * BN + i / CH;
-            pages[it] = (i < BN * CH && j >= key_begin && j < key_end) ? bt[page_of(j)] : -1;
+            pages[it] = (i < BN * CH && (j >= key_begin || j < keep_first) && j < key_end) ? bt[page_of(j)] : -1;
         }
 #pragma unroll
         for (int it = 0; it < KV_ITERS; ++it) {
@@ -97,13 +115,13 @@ attention_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part
             if (i >= BN * CH) break;
             const int row = i / CH, chunk = i % CH, j = kb * BN + row;
             int page = pages[it];
-            if (j >= key_begin && j < key_end && (page < 0 || page >= num_pages)) { atomicOr(err, CELLM_DEV_BAD_PAGE); page = -1; }
+            if ((j >= key_begin || j < keep_first) && j < key_end && (page < 0 || page >= num_pages)) { atomicOr(err, CELLM_DEV_BAD_PAGE); page = -1; }
             const size_t off = page >= 0 ? (size_t)page * page_elems + ((size_t)kvh * page_size + slot_of(j)) * HD + chunk * 8 : 0;
             cp_async16(ks + tile_offset<HD>(row, chunk), k_pool + off, page >= 0 ? 16 : 0);
             cp_async16(vs + tile_offset<HD>(row, chunk), v_pool + off, page >= 0 ? 16 : 0);
         }
     };
-    if (my_begin < my_end) load_kv(my_begin, 0);
+    if (my_begin < my_end) load_kv(block_of(my_begin), 0);
     cp_async_commit();
 
     // per-thread rows: g = lane / 4 and g + 8 of this warp's 16
@@ -117,9 +135,9 @@ attention_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part
     uint32_t qf[HD / 16][4];
     bool q_loaded = false;
 
-    for (int kb = my_begin, it = 0; kb < my_end; ++kb, ++it) {
-        const int stage = it & 1;
-        if (kb + 1 < my_end) load_kv(kb + 1, stage ^ 1);
+    for (int vi = my_begin, it = 0; vi < my_end; ++vi, ++it) {
+        const int stage = it & 1, kb = block_of(vi);
+        if (vi + 1 < my_end) load_kv(block_of(vi + 1), stage ^ 1);
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
@@ -164,8 +182,8 @@ attention_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int j = j0 + n * 8 + e;
-                    const float va = (j <= pos_a && j >= lo_a) ? s[n][e] : -INFINITY;
-                    const float vb = (j <= pos_b && j >= lo_b) ? s[n][2 + e] : -INFINITY;
+                    const float va = (j <= pos_a && (j >= lo_a || j < keep_first)) ? s[n][e] : -INFINITY;
+                    const float vb = (j <= pos_b && (j >= lo_b || j < keep_first)) ? s[n][2 + e] : -INFINITY;
                     s[n][e] = va;
                     s[n][2 + e] = vb;
                     mx_a = fmaxf(mx_a, va);
@@ -224,7 +242,11 @@ attention_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part
             if (row_a < rows) l_a += exp2f(sinks[kvh * G + row_a % G] * 1.4426950408889634f - (m_a == -INFINITY ? 0.f : m_a));
             if (row_b < rows) l_b += exp2f(sinks[kvh * G + row_b % G] * 1.4426950408889634f - (m_b == -INFINITY ? 0.f : m_b));
         }
-        const float inv_a = l_a > 0.f ? 1.0f / l_a : 0.f, inv_b = l_b > 0.f ? 1.0f / l_b : 0.f;
+        float inv_a = l_a > 0.f ? 1.0f / l_a : 0.f, inv_b = l_b > 0.f ? 1.0f / l_b : 0.f;
+        if (ex.gate) {
+            if (row_a < rows) inv_a *= gate_factor(ex, t_base + row_a / G, kvh * G + row_a % G);
+            if (row_b < rows) inv_b *= gate_factor(ex, t_base + row_b / G, kvh * G + row_b % G);
+        }
         if (unrot) {
             // values were cached turned by their own positions: a row's sum is turned back by the row's position
 #pragma unroll
@@ -302,7 +324,7 @@ attention_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part
 __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o,
                                        const float* __restrict__ part_ml, size_t n_rows, int hd, int nsplit,
                                        const float* __restrict__ sinks, const float* __restrict__ unrot,
-                                       int interleaved, const int* __restrict__ positions, int nh) {
+                                       int interleaved, const int* __restrict__ positions, int nh, const FlashExtras ex) {
     pdl_trigger();
     pdl_wait();
     const size_t row = blockIdx.x;
@@ -313,7 +335,7 @@ __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const fl
     for (int s = 0; s < nsplit; ++s)
         l += exp2f(part_ml[((size_t)s * n_rows + row) * 2] - use) * part_ml[((size_t)s * n_rows + row) * 2 + 1];
     if (sinks) l += exp2f(sinks[row % nh] * 1.4426950408889634f - use);
-    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    const float inv = (l > 0.f ? 1.0f / l : 0.f) * gate_factor(ex, (int)(row / nh), (int)(row % nh));
     if (unrot) {
         // a thread a pair: the merged sum is turned back by the row's position
         const float fp = (float)positions[row / nh];
@@ -349,7 +371,8 @@ template <int HD, int NWARPS>
 int launch_flash(__nv_bfloat16* out, float* part_o, float* part_ml, const __nv_bfloat16* q, const __nv_bfloat16* k_pool,
                  const __nv_bfloat16* v_pool, const int* cu, const int* ctx, const int* bt, int bt_stride, int B, int T,
                  int n_tiles, int num_pages, int page_size, int nh, int nkv, float scale, int window, int nsplit,
-                 int* err, cudaStream_t stream, const float* sinks = nullptr, const float* unrot = nullptr, int interleaved = 0) {
+                 int* err, cudaStream_t stream, const float* sinks = nullptr, const float* unrot = nullptr, int interleaved = 0,
+                 FlashExtras ex = FlashExtras()) {
     constexpr int BM = 16 * NWARPS;
     const size_t smem = (size_t)(BM + 4 * FA_BN) * HD * 2;
     static bool configured = false;
@@ -361,7 +384,7 @@ int launch_flash(__nv_bfloat16* out, float* part_o, float* part_ml, const __nv_b
     dim3 grid((unsigned)n_tiles, (unsigned)nkv, (unsigned)nsplit);
     CELLM_RUN((attention_flash_kernel<HD, NWARPS>), grid, NWARPS * 32, smem, stream,
               out, part_o, part_ml, q, k_pool, v_pool, cu, ctx, bt, bt_stride, B, T, num_pages, page_size, nh, nkv,
-              scale * 1.4426950408889634f, window, sinks, unrot, interleaved, err);
+              scale * 1.4426950408889634f, window, sinks, unrot, interleaved, ex, err);
     return CELLM_OK;
 }
 
@@ -378,8 +401,9 @@ static int attention_flash_impl(void* out, float* part_o, float* part_ml, const 
                                 const int* block_table, int bt_stride, int B, int T, int n_tiles, int num_pages,
                                 int page_size, int nh, int nkv, int hd, float scale, int window, int wide,
                                 int nsplit, int* err, cudaStream_t stream, const float* sinks, const float* unrot,
-                                int interleaved, const int* positions) {
+                                int interleaved, const int* positions, FlashExtras ex = FlashExtras()) {
     if (T <= 0 || n_tiles <= 0) return CELLM_OK;
+    if (ex.keep_first < 0) return CELLM_ERR_SIZE;
     if (unrot && nsplit > 1 && !positions) return CELLM_ERR_ARG;
     if (nkv <= 0 || nh % nkv) return CELLM_ERR_SIZE;
     if (nsplit < 1 || (nsplit > 1 && (!part_o || !part_ml))) return CELLM_ERR_ARG;
@@ -389,11 +413,11 @@ static int attention_flash_impl(void* out, float* part_o, float* part_ml, const 
     rc = wide ? launch_flash<HD_, 4>((__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q,               \
                                      (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, cu_seqlens,      \
                                      ctx_lens, block_table, bt_stride, B, T, n_tiles, num_pages, page_size, nh,   \
-                                     nkv, scale, window, nsplit, err, stream, sinks, unrot, interleaved)          \
+                                     nkv, scale, window, nsplit, err, stream, sinks, unrot, interleaved, ex)          \
               : launch_flash<HD_, 1>((__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q,               \
                                      (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, cu_seqlens,      \
                                      ctx_lens, block_table, bt_stride, B, T, n_tiles, num_pages, page_size, nh,   \
-                                     nkv, scale, window, nsplit, err, stream, sinks, unrot, interleaved)
+                                     nkv, scale, window, nsplit, err, stream, sinks, unrot, interleaved, ex)
     if (hd == 32) GO(32);
     else if (hd == 64) GO(64);
     else if (hd == 128) GO(128);
@@ -403,7 +427,7 @@ static int attention_flash_impl(void* out, float* part_o, float* part_ml, const 
     if (nsplit > 1) {
         CELLM_RUN(attention_merge_kernel, (unsigned)((size_t)T * nh), hd >= 64 ? 64 : 32, 0, stream,
                   (__nv_bfloat16*)out, (const float*)part_o, (const float*)part_ml, (size_t)T * nh, hd, nsplit, sinks, unrot,
-                  interleaved, positions, nh);
+                  interleaved, positions, nh, ex);
     }
     return CELLM_OK;
 }
@@ -431,6 +455,24 @@ CELLM_API int cellm_attention_flash_sink(void* out, float* part_o, float* part_m
     return attention_flash_impl(out, part_o, part_ml, q, k_pool, v_pool, cu_seqlens, ctx_lens, block_table, bt_stride, B, T,
                                 n_tiles, num_pages, page_size, nh, nkv, hd, scale, window, wide, nsplit, err, stream, sinks,
                                 unrot, interleaved, positions);
+}
+
+// The general form: a learned sink per head (`sinks`; a fixed sink is a vector of one score), the sequence's first
+// `keep_first` keys visible behind the window (position i sees j <= i with i - j < window or j < keep_first), and an output
+// gate (`gate` [T, gate_ld] 32-bit pre-activations, one per head; null: none).
+CELLM_API int cellm_attention_flash_masked(void* out, float* part_o, float* part_ml, const void* q, const void* k_pool,
+                                           const void* v_pool, const int* cu_seqlens, const int* ctx_lens,
+                                           const int* block_table, int bt_stride, int B, int T, int n_tiles, int num_pages,
+                                           int page_size, int nh, int nkv, int hd, float scale, int window, int keep_first,
+                                           int wide, int nsplit, const float* sinks, const float* gate, long long gate_ld,
+                                           int* err, cudaStream_t stream) {
+    FlashExtras ex;
+    ex.keep_first = window > 0 ? keep_first : 0;
+    ex.gate = gate;
+    ex.gate_ld = gate_ld;
+    return attention_flash_impl(out, part_o, part_ml, q, k_pool, v_pool, cu_seqlens, ctx_lens, block_table, bt_stride, B, T,
+                                n_tiles, num_pages, page_size, nh, nkv, hd, scale, window, wide, nsplit, err, stream, sinks,
+                                nullptr, 0, nullptr, ex);
 }
 
 // ---------------------------------------------------------------------------

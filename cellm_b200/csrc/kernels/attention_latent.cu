@@ -25,7 +25,7 @@ latent_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
                     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pool,
                     const int* __restrict__ cu_seqlens, const int* __restrict__ ctx_lens, const int* __restrict__ block_table,
                     int bt_stride, int B, int T, int num_pages, int page_size, int nh, int kw, int dv, float scale_log2e,
-                    int nsplit, int* __restrict__ err) {
+                    int nsplit, int window, const float* __restrict__ sinks, int* __restrict__ err) {
     constexpr int NT = DVW / 8;
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const int stride = kw + 8;                                   // elements per row in shared memory (16 bytes of padding)
@@ -50,9 +50,11 @@ latent_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
     const int r0 = tile * LA_BM;
     const int t_hi = min(r0 + LA_BM - 1, rows - 1) / nh;
     const int key_end = ctx + t_hi + 1;
-    const int kb_end = (key_end + BN - 1) / BN;
-    const int per = (kb_end + nsplit - 1) / nsplit;
-    const int my_begin = split * per, my_end = min(kb_end, my_begin + per);
+    // with a window a row reads its last `window` rows only: the tile's first key is its first row's
+    const int key_begin = window > 0 ? max(0, ctx + r0 / nh - window + 1) : 0;
+    const int kb_begin = key_begin / BN, kb_end = (key_end + BN - 1) / BN;
+    const int per = (kb_end - kb_begin + nsplit - 1) / nsplit;
+    const int my_begin = kb_begin + split * per, my_end = min(kb_end, my_begin + per);
     const int* bt = block_table + (size_t)b * bt_stride;
     pdl_wait();
 
@@ -69,7 +71,7 @@ latent_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
         if (threadIdx.x < BN) {
             const int j = kb * BN + threadIdx.x;
             long long at = -1;
-            if (j < key_end) {
+            if (j >= key_begin && j < key_end) {
                 const int page = bt[j / page_size];
                 if (page < 0 || page >= num_pages) atomicOr(err, CELLM_DEV_BAD_PAGE);
                 else at = ((long long)page * page_size + j % page_size) * kw;
@@ -89,6 +91,7 @@ latent_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
 
     const int row_a = r0 + rw * 16 + (lane >> 2), row_b = row_a + 8;
     const int pos_a = row_a < rows ? ctx + row_a / nh : -1, pos_b = row_b < rows ? ctx + row_b / nh : -1;
+    const int lo_a = window > 0 ? pos_a - window + 1 : 0, lo_b = window > 0 ? pos_b - window + 1 : 0;
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
     float o[NT][4];
 #pragma unroll
@@ -106,6 +109,7 @@ latent_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
 #pragma unroll 1
         for (int sub = 0; sub < BN / SUB; ++sub) {
         if ((kb * BN + sub * SUB) >= key_end) break;
+        if (kb * BN + sub * SUB + SUB <= key_begin) continue;
         const __nv_bfloat16* ks_ = k_s + (stage * BN + sub * SUB) * stride;
         float s[SUB / 8][4];
 #pragma unroll
@@ -132,8 +136,8 @@ latent_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int j = j0 + n * 8 + e;
-                const float va = j <= pos_a ? s[n][e] : -INFINITY;
-                const float vb = j <= pos_b ? s[n][2 + e] : -INFINITY;
+                const float va = (j <= pos_a && j >= lo_a) ? s[n][e] : -INFINITY;
+                const float vb = (j <= pos_b && j >= lo_b) ? s[n][2 + e] : -INFINITY;
                 s[n][e] = va;
                 s[n][2 + e] = vb;
                 mx_a = fmaxf(mx_a, va);
@@ -189,6 +193,11 @@ latent_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
     const int col = cg * DVW + (lane & 3) * 2;
     const size_t base_row = (size_t)t_base * nh;
     if (nsplit == 1) {
+        if (sinks) {
+            // a sink: one more term exp(sink_h) in the row's denominator, with no key and no value
+            if (row_a < rows) l_a += exp2f(sinks[row_a % nh] * 1.4426950408889634f - (m_a == -INFINITY ? 0.f : m_a));
+            if (row_b < rows) l_b += exp2f(sinks[row_b % nh] * 1.4426950408889634f - (m_b == -INFINITY ? 0.f : m_b));
+        }
         const float inv_a = l_a > 0.f ? 1.0f / l_a : 0.f, inv_b = l_b > 0.f ? 1.0f / l_b : 0.f;
         if (row_a < rows) {
             __nv_bfloat16* dst = out + (base_row + row_a) * dv + col;
@@ -221,7 +230,8 @@ latent_flash_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
 
 // The pieces of a row merged in their order: out = sum_s 2^(m_s - M) o_s / sum_s 2^(m_s - M) l_s.
 __global__ void latent_merge_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o,
-                                    const float* __restrict__ part_ml, size_t n_rows, int dv, int nsplit) {
+                                    const float* __restrict__ part_ml, size_t n_rows, int dv, int nsplit,
+                                    const float* __restrict__ sinks, int nh) {
     extern __shared__ float ml[];        // [nsplit][2]: maximum and sum of each piece, then its weight in [s][0]
     pdl_trigger();
     pdl_wait();
@@ -236,6 +246,7 @@ __global__ void latent_merge_kernel(__nv_bfloat16* __restrict__ out, const float
     for (int s = 0; s < nsplit; ++s) M = fmaxf(M, ml[2 * s]);
     float L = 0.f;
     for (int s = 0; s < nsplit; ++s) L += ml[2 * s] == -INFINITY ? 0.f : fast_exp2(ml[2 * s] - M) * ml[2 * s + 1];   // in the pieces' order
+    if (sinks) L += exp2f(sinks[r % nh] * 1.4426950408889634f - (M == -INFINITY ? 0.f : M));          // the sink counts once
     const float inv = L > 0.f ? 1.0f / L : 0.f;
     for (int d = threadIdx.x; d < dv; d += blockDim.x) {
         float acc = 0.f;
@@ -334,13 +345,14 @@ CELLM_API int cellm_attention_latent_supports(int kw, int dv) {
 
 // q: [T, nh, kw] (a head's query against the cached rows); out: [T, nh, dv]; pool: one layer's rows. part_o
 // [nsplit, T * nh, dv] and part_ml [nsplit, T * nh, 2] floats are needed when nsplit > 1. n_tiles: the sum over the
-// requests of ceil(tokens * nh / 64).
+// requests of ceil(tokens * nh / 64). window: 0, or how many of its last rows a token reads (itself included). sinks [nh]
+// 32-bit: one more term exp(sink_h) in a head's denominator (null: none).
 CELLM_API int cellm_attention_latent(void* out, float* part_o, float* part_ml, const void* q, const void* pool,
                                      const int* cu_seqlens, const int* ctx_lens, const int* block_table, int bt_stride, int B,
                                      int T, int n_tiles, int num_pages, int page_size, int nh, int kw, int dv, float scale,
-                                     int nsplit, int* err, cudaStream_t stream) {
+                                     int nsplit, int window, const float* sinks, int* err, cudaStream_t stream) {
     if (T <= 0 || B <= 0 || n_tiles <= 0) return CELLM_OK;
-    if (!cellm_attention_latent_supports(kw, dv) || nh <= 0 || page_size <= 0 || nsplit < 1 || !(scale > 0.f)) return CELLM_ERR_SIZE;
+    if (!cellm_attention_latent_supports(kw, dv) || nh <= 0 || page_size <= 0 || nsplit < 1 || !(scale > 0.f) || window < 0) return CELLM_ERR_SIZE;
     if (((uintptr_t)q & 15) || ((uintptr_t)pool & 15) || ((uintptr_t)out & 3)) return CELLM_ERR_ALIGN;
     if (nsplit > 1 && (!part_o || !part_ml)) return CELLM_ERR_ARG;
     const int dvw = value_columns(dv), bn = keys_per_block(dvw, kw);
@@ -354,7 +366,7 @@ CELLM_API int cellm_attention_latent(void* out, float* part_o, float* part_ml, c
             cudaFuncSetAttribute(latent_flash_kernel<DVW, BN, SUB, MAXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         CELLM_RUN((latent_flash_kernel<DVW, BN, SUB, MAXT>), grid, threads, smem, stream, (__nv_bfloat16*)out, part_o, part_ml,  \
                   (const __nv_bfloat16*)q, (const __nv_bfloat16*)pool, cu_seqlens, ctx_lens, block_table, bt_stride, B, T,  \
-                  num_pages, page_size, nh, kw, dv, scale_log2e, nsplit, err);                                             \
+                  num_pages, page_size, nh, kw, dv, scale_log2e, nsplit, window, sinks, err);                               \
     } while (0)
     if (dvw == 256 && bn == 64) LAUNCH(256, 64, 32, 256);
     else if (dvw == 256) LAUNCH(256, 32, 32, 256);
@@ -365,7 +377,7 @@ CELLM_API int cellm_attention_latent(void* out, float* part_o, float* part_ml, c
 #undef LAUNCH
     if (nsplit > 1)
         CELLM_RUN(latent_merge_kernel, (unsigned)((size_t)T * nh), dv >= 256 ? 256 : (dv >= 128 ? 128 : 64), (size_t)nsplit * 2 * sizeof(float), stream, (__nv_bfloat16*)out, part_o,
-                  part_ml, (size_t)T * nh, dv, nsplit);
+                  part_ml, (size_t)T * nh, dv, nsplit, sinks, nh);
     return CELLM_OK;
 }
 

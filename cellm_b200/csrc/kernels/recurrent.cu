@@ -58,24 +58,28 @@ __device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.com
 template <int N> __device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // Where the vectors over a head's rows lie: array a of token t and head h starts at p[a] + t * ld[a] + (h / heads_per[a]) * dim.
-// Delta rule: q, k, decay. HGRN2: q, f.
+// Delta rule: q, k, decay. HGRN2: q, f. Generalized delta rule: r, k, decay, unit key, removal rate times unit key.
 struct WalkVectors {
-    const float* p[3];
-    long long ld[3];
-    int heads_per[3];
+    const float* p[5];
+    long long ld[5];
+    int heads_per[5];
     int vec16;          // every start is a multiple of 16 bytes: copies of four values
 };
 
-template <int DIM, int ROWS, bool DELTA>
+// MODE 0: HGRN2; 1: the gated delta rule; 2: the generalized delta rule (five vectors a token: chunks of four tokens for
+// heads of 128 rows, so that three stages stay within the static shared memory).
+template <int DIM, int ROWS, int MODE>
 __global__ void __launch_bounds__(WALK_THREADS)
 state_walk_kernel(float* __restrict__ o_out, float* __restrict__ state, long long slot_stride, int n_slots, const WalkVectors vec,
                   const float* __restrict__ v_in, long long ld_v, const float* __restrict__ beta,
                   const int* __restrict__ cu_seqlens, const int* __restrict__ slot_ids, int heads, int dim, int vd,
                   int* __restrict__ err) {
     using W = WalkShape<DIM, ROWS>;
-    constexpr int RG = W::RG, CPB = W::CPB, NV = DELTA ? 3 : 2, NG = ROWS / 4;
+    constexpr bool DELTA = MODE == 1;
+    constexpr int RG = W::RG, CPB = W::CPB, NV = MODE == 2 ? 5 : (DELTA ? 3 : 2), NG = ROWS / 4;
+    constexpr int CHUNK = (MODE == 2 && DIM > 64) ? 4 : WALK_CHUNK;
     constexpr int TOK = NV * DIM + CPB + 4;          // a token in a stage: its vectors | the block's entries of v | beta
-    __shared__ __align__(16) float buf[WALK_STAGES][WALK_CHUNK * TOK];
+    __shared__ __align__(16) float buf[WALK_STAGES][CHUNK * TOK];
     __shared__ float tile[DIM][CPB + 1];             // the block's columns of S on their way in and out
     const int b = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int r = lane % RG, cl = warp * W::CPW + lane / RG, col0 = blockIdx.z * CPB, j = col0 + cl;
@@ -88,13 +92,13 @@ state_walk_kernel(float* __restrict__ o_out, float* __restrict__ state, long lon
     float* st = state + (size_t)slot * slot_stride + (size_t)h * dim * vd;
     const bool live = j < vd;
     if (dim < DIM) {            // the rows beyond the head's own stay zero in every stage
-        for (int i = tid; i < WALK_STAGES * WALK_CHUNK * TOK; i += WALK_THREADS) (&buf[0][0])[i] = 0.f;
+        for (int i = tid; i < WALK_STAGES * CHUNK * TOK; i += WALK_THREADS) (&buf[0][0])[i] = 0.f;
         __syncthreads();
     }
-    const int n_chunks = (end - start + WALK_CHUNK - 1) / WALK_CHUNK;
+    const int n_chunks = (end - start + CHUNK - 1) / CHUNK;
     auto issue = [&](int c) {
         float* dst = buf[c % WALK_STAGES];
-        const int t0 = start + c * WALK_CHUNK, nt = min(WALK_CHUNK, end - t0);
+        const int t0 = start + c * CHUNK, nt = min(CHUNK, end - t0);
 #pragma unroll
         for (int a = 0; a < NV; ++a) {
             const float* src = vec.p[a] + (size_t)t0 * vec.ld[a] + (h / vec.heads_per[a]) * dim;
@@ -135,7 +139,29 @@ state_walk_kernel(float* __restrict__ o_out, float* __restrict__ state, long lon
         const float4* q4 = reinterpret_cast<const float4*>(tok);
         const float v = tok[NV * DIM + cl];
         float o0 = 0.f, o1 = 0.f;
-        if constexpr (DELTA) {
+        if constexpr (MODE == 2) {
+            // S <- diag(d) S - (a u)(u^T S) + k v^T, both terms over the old S: the sum u^T S over the column's rows first
+            const float4* k4 = reinterpret_cast<const float4*>(tok + DIM);
+            const float4* d4 = reinterpret_cast<const float4*>(tok + 2 * DIM);
+            const float4* u4 = reinterpret_cast<const float4*>(tok + 3 * DIM);
+            const float4* a4 = reinterpret_cast<const float4*>(tok + 4 * DIM);
+            float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+            for (int g = 0; g < NG; ++g) {
+                const float4 u = u4[g * RG + r];
+                a0 = fmaf(S[4 * g + 0], u.x, a0), a1 = fmaf(S[4 * g + 1], u.y, a1);
+                a0 = fmaf(S[4 * g + 2], u.z, a0), a1 = fmaf(S[4 * g + 3], u.w, a1);
+            }
+            const float dot = -sum_over_rows<RG>(a0 + a1);
+#pragma unroll
+            for (int g = 0; g < NG; ++g) {
+                const float4 q = q4[g * RG + r], k = k4[g * RG + r], d = d4[g * RG + r], au = a4[g * RG + r];
+                S[4 * g + 0] = fmaf(k.x, v, fmaf(d.x, S[4 * g + 0], au.x * dot)), S[4 * g + 1] = fmaf(k.y, v, fmaf(d.y, S[4 * g + 1], au.y * dot));
+                S[4 * g + 2] = fmaf(k.z, v, fmaf(d.z, S[4 * g + 2], au.z * dot)), S[4 * g + 3] = fmaf(k.w, v, fmaf(d.w, S[4 * g + 3], au.w * dot));
+                o0 = fmaf(S[4 * g + 0], q.x, o0), o1 = fmaf(S[4 * g + 1], q.y, o1);
+                o0 = fmaf(S[4 * g + 2], q.z, o0), o1 = fmaf(S[4 * g + 3], q.w, o1);
+            }
+        } else if constexpr (DELTA) {
             const float4* k4 = reinterpret_cast<const float4*>(tok + DIM);
             const float4* g4 = reinterpret_cast<const float4*>(tok + 2 * DIM);
             const float bt = tok[NV * DIM + CPB];
@@ -179,24 +205,24 @@ state_walk_kernel(float* __restrict__ o_out, float* __restrict__ state, long lon
         if (c + WALK_STAGES - 1 < n_chunks) issue(c + WALK_STAGES - 1);
         copy_async_commit();
         const float* stage = buf[c % WALK_STAGES];
-        const int t0 = start + c * WALK_CHUNK, nt = min(WALK_CHUNK, end - t0);
-        if (nt == WALK_CHUNK) {
+        const int t0 = start + c * CHUNK, nt = min(CHUNK, end - t0);
+        if (nt == CHUNK) {
             // a whole chunk: the tokens' read-outs wait as the lanes' shares and are summed over the lanes together, step
             // by step, so that a shuffle's latency is paid once a chunk and not once a token (the same sums in the same order)
-            float share[WALK_CHUNK];
+            float share[CHUNK];
 #pragma unroll
-            for (int tt = 0; tt < WALK_CHUNK; ++tt) share[tt] = token(stage + tt * TOK);
+            for (int tt = 0; tt < CHUNK; ++tt) share[tt] = token(stage + tt * TOK);
 #pragma unroll
             for (int d = 1; d < RG; d <<= 1) {
-                float other[WALK_CHUNK];
+                float other[CHUNK];
 #pragma unroll
-                for (int tt = 0; tt < WALK_CHUNK; ++tt) other[tt] = __shfl_xor_sync(0xffffffffu, share[tt], d);
+                for (int tt = 0; tt < CHUNK; ++tt) other[tt] = __shfl_xor_sync(0xffffffffu, share[tt], d);
 #pragma unroll
-                for (int tt = 0; tt < WALK_CHUNK; ++tt) share[tt] += other[tt];
+                for (int tt = 0; tt < CHUNK; ++tt) share[tt] += other[tt];
             }
             if (live && r == 0) {
 #pragma unroll
-                for (int tt = 0; tt < WALK_CHUNK; ++tt) o_col[(size_t)(t0 + tt) * o_ld] = share[tt];
+                for (int tt = 0; tt < CHUNK; ++tt) o_col[(size_t)(t0 + tt) * o_ld] = share[tt];
             }
         } else {
             for (int tt = 0; tt < nt; ++tt) {
@@ -334,12 +360,11 @@ CELLM_API int cellm_hgrn2_scan(float* o_out, float* state, long long slot_stride
     CELLM_RUN(hgrn2_gates_kernel, (unsigned)std::min<size_t>((total + 255) / 256, 148 * 16), 256, 0, stream, proj, ld, col_q, col_f, f_bias,
               lower, T, heads * dim);
     WalkVectors vec;
-    vec.p[0] = proj + col_q, vec.p[1] = proj + col_f, vec.p[2] = nullptr;
-    vec.ld[0] = vec.ld[1] = vec.ld[2] = ld;
-    vec.heads_per[0] = vec.heads_per[1] = vec.heads_per[2] = 1;
+    for (int a = 0; a < 5; ++a) vec.p[a] = nullptr, vec.ld[a] = ld, vec.heads_per[a] = 1;
+    vec.p[0] = proj + col_q, vec.p[1] = proj + col_f;
     vec.vec16 = dim % 4 == 0 && ld % 4 == 0 && aligned16(vec.p[0]) && aligned16(vec.p[1]);
 #define HGRN2_WALK(D, R)                                                                                           \
-    CELLM_RUN((state_walk_kernel<D, R, false>), dim3(B, heads, (vd + WalkShape<D, R>::CPB - 1) / WalkShape<D, R>::CPB), WALK_THREADS, 0, stream, \
+    CELLM_RUN((state_walk_kernel<D, R, 0>), dim3(B, heads, (vd + WalkShape<D, R>::CPB - 1) / WalkShape<D, R>::CPB), WALK_THREADS, 0, stream, \
               o_out, state, slot_stride, n_slots, vec, (const float*)(proj + col_v), ld, (const float*)nullptr, cu_seqlens, slot_ids,  \
               heads, dim, vd, err)
     if (dim <= 16) HGRN2_WALK(16, 4);
@@ -496,12 +521,13 @@ CELLM_API int cellm_delta_scan(float* o_out, float* state, long long slot_stride
     if (B <= 0) return CELLM_OK;
     if (heads <= 0 || kvh <= 0 || heads % kvh || dim <= 0 || vd <= 0 || dim > RECURRENT_MAX_DIM) return CELLM_ERR_SIZE;
     WalkVectors vec;
+    for (int a = 0; a < 5; ++a) vec.p[a] = nullptr, vec.ld[a] = 0, vec.heads_per[a] = 1;
     vec.p[0] = qk, vec.p[1] = qk + (size_t)kvh * dim, vec.p[2] = decay;
     vec.ld[0] = vec.ld[1] = 2LL * kvh * dim, vec.ld[2] = (long long)heads * dim;
     vec.heads_per[0] = vec.heads_per[1] = heads / kvh, vec.heads_per[2] = 1;
     vec.vec16 = dim % 4 == 0 && aligned16(qk) && aligned16(decay);
 #define DELTA_WALK(D, R)                                                                                           \
-    CELLM_RUN((state_walk_kernel<D, R, true>), dim3(B, heads, (vd + WalkShape<D, R>::CPB - 1) / WalkShape<D, R>::CPB), WALK_THREADS, 0, stream, \
+    CELLM_RUN((state_walk_kernel<D, R, 1>), dim3(B, heads, (vd + WalkShape<D, R>::CPB - 1) / WalkShape<D, R>::CPB), WALK_THREADS, 0, stream, \
               o_out, state, slot_stride, n_slots, vec, v_in, (long long)heads * vd, beta, cu_seqlens, slot_ids, heads, dim, vd, err)
     if (dim <= 16) DELTA_WALK(16, 4);
     else if (dim <= 32) DELTA_WALK(32, 4);
@@ -605,7 +631,7 @@ gdelta_scan_kernel(float* __restrict__ o_out, float* __restrict__ state, long lo
         for (int i = 0; i < dim; ++i) dot = fmaf(us[i], S(i), dot);
         float o = 0.f;
         for (int i = 0; i < dim; ++i) {
-            const float s_new = fmaf(ks[i], v, fmaf(ds[i], S(i), -as[i] * dot));
+            const float s_new = fmaf(ks[i], v, fmaf(ds[i], S(i), as[i] * -dot));
             S(i) = s_new;
             o = fmaf(s_new, rs[i], o);
         }
@@ -623,6 +649,24 @@ CELLM_API int cellm_gdelta_scan(float* o_out, float* state, long long slot_strid
                                 int B, int heads, int dim, int vd, int* err, cudaStream_t stream) {
     if (B <= 0) return CELLM_OK;
     if (heads <= 0 || dim <= 0 || vd <= 0 || dim > RECURRENT_MAX_DIM) return CELLM_ERR_SIZE;
+    if (dim <= 128) {       // the head's columns in registers (state_walk_kernel)
+        const long long HD = (long long)heads * dim;
+        WalkVectors vec;
+        vec.p[0] = proj + col_r, vec.p[1] = proj + col_k, vec.p[2] = vecs, vec.p[3] = vecs + HD, vec.p[4] = vecs + 2 * HD;
+        vec.ld[0] = vec.ld[1] = ld, vec.ld[2] = vec.ld[3] = vec.ld[4] = 3 * HD;
+        for (int a = 0; a < 5; ++a) vec.heads_per[a] = 1;
+        vec.vec16 = dim % 4 == 0 && ld % 4 == 0 && aligned16(vec.p[0]) && aligned16(vec.p[1]) && aligned16(vecs);
+#define GDELTA_WALK(D, R)                                                                                          \
+    CELLM_RUN((state_walk_kernel<D, R, 2>), dim3(B, heads, (vd + WalkShape<D, R>::CPB - 1) / WalkShape<D, R>::CPB), WALK_THREADS, 0, stream, \
+              o_out, state, slot_stride, n_slots, vec, (const float*)(proj + col_v), ld, (const float*)nullptr, cu_seqlens, slot_ids,  \
+              heads, dim, vd, err)
+        if (dim <= 16) GDELTA_WALK(16, 4);
+        else if (dim <= 32) GDELTA_WALK(32, 4);
+        else if (dim <= 64) GDELTA_WALK(64, 8);
+        else GDELTA_WALK(128, 8);
+#undef GDELTA_WALK
+        return CELLM_OK;
+    }
     const size_t smem = (size_t)(5 + 32) * dim * sizeof(float);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(gdelta_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -56,7 +56,8 @@ typedef int (*GatedActFn)(P h, CP gu, i64 ld, CP bg, CP bu, int w_tag, int T, in
 typedef int (*BiasAddFn)(P out, CP in, CP b, int w_tag, int T, int N, int tag, P stream);
 typedef int (*HeadProductMmaFn)(P out, i64 ldo, i64 out_hs, CP in, i64 ldi, i64 in_hs, CP w, int T, int heads, int N, int K, P stream);
 typedef int (*AttentionLatentFn)(P out, P part_o, P part_ml, CP q, CP pool, CP cu, CP ctx, CP bt, int bt_stride, int B, int T, int n_tiles,
-                                 int pages, int page_size, int nh, int kw, int dv, float scale, int nsplit, P err, P stream);
+                                 int pages, int page_size, int nh, int kw, int dv, float scale, int nsplit, int window, CP sinks, P err,
+                                 P stream);
 typedef int (*EmbedPosFn)(P out, CP table, int tag, CP ids, CP pos_table, CP positions, int max_pos, int T, int H, int V, float scale, P err,
                           P stream);
 typedef int (*AttnPrepFn)(P q, CP qkv, i64 row_stride, CP q_w, CP k_w, int w_tag, float eps, int span, float temp_coef, int temp_every,
@@ -811,10 +812,10 @@ void Run::latent_attention(const LatentAttentionParams& L, const ExecItem& it, c
     else if (L.rank % 32 == 0 && L.rank / 32 <= 8) dvw = 32;
     else if (L.rank % 16 == 0 && L.rank / 16 <= 8) dvw = 16;
     const i64 bn = dvw == 256 ? ((64 + 128) * (kw + 8) * 2 + 2048 <= 227 * 1024 ? 64 : 32) : (dvw == 64 ? 64 : 32);
-    if (p.latent_tc && act == EXEC_BF16 && L.scale > 0 && !L.window && !L.sinks && dvw && kw % 16 == 0 && (64 + 2 * bn) * (kw + 8) * 2 + 2048 <= 227 * 1024) {
+    if (p.latent_tc && act == EXEC_BF16 && L.scale > 0 && dvw && kw % 16 == 0 && (64 + 2 * bn) * (kw + 8) * 2 + 2048 <= 227 * 1024) {
         i64 n_tiles = 0;
         for (i64 b = 0; b < s.B; ++b) n_tiles += ceil_div(s.q_lens[b] * nh, 64);
-        const i64 blocks = ceil_div(s.max_total_len, bn);
+        const i64 blocks = ceil_div(L.window ? std::min<i64>(s.max_total_len, L.window + s.max_q_len) : s.max_total_len, bn);
         // pieces of the keys: what fills the SMs once (two CTAs an SM where two tiles of this width fit its shared
         // memory), of at least two blocks of keys each
         const i64 per_sm = std::min<i64>(2, std::max<i64>(1, 227 * 1024 / ((64 + 2 * bn) * (kw + 8) * 2)));
@@ -831,7 +832,7 @@ void Run::latent_attention(const LatentAttentionParams& L, const ExecItem& it, c
         LAUNCH(fn<AttentionLatentFn>(FN_ATTENTION_LATENT)(o_lat, part_o, part_ml, q_full, it.k, s.cu_seqlens, s.ctx_lens, it.block_table,
                                                       (int)it.bt_stride, (int)s.B, (int)T, (int)n_tiles, (int)it.num_pages,
                                                       (int)it.page_size, (int)nh, (int)kw, (int)L.rank, (float)L.scale, (int)nsplit,
-                                                      s.err, s.stream),
+                                                      (int)L.window, L.sinks, s.err, s.stream),
                "attention_latent");
         if (nsplit > 1) ++launches;                    // the merge of the pieces
     } else if (L.window || L.sinks)

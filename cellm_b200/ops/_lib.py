@@ -83,9 +83,10 @@ _SIGNATURES = {
         "cellm_attention_flash": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, I, P, P],
         "cellm_attention_flash_supports": [I],
         "cellm_attention_flash_sink": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, I, P, P, I, P, P, P],
+        "cellm_attention_flash_masked": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, I, I, P, P, L, P, P],
     },
     "attention_latent": {
-        "cellm_attention_latent": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P],
+        "cellm_attention_latent": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, P, P, P],
         "cellm_attention_latent_supports": [I, I],
         "cellm_head_product_mma": [P, L, L, P, L, L, P, I, I, I, I, P],
     },

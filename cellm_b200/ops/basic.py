@@ -280,10 +280,11 @@ def gated_act(gu: torch.Tensor, bg: Optional[torch.Tensor], bu: Optional[torch.T
 
 def attention_latent(q: torch.Tensor, pool: torch.Tensor, cu_seqlens: torch.Tensor, ctx_lens: torch.Tensor,
                      block_table: torch.Tensor, q_lens, nh: int, dv: int, scale: float, nsplit: int,
-                     err: torch.Tensor) -> torch.Tensor:
+                     err: torch.Tensor, window: int = 0, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The tensor-core attention over a latent cache by itself: q [T, nh * kw] bfloat16, pool [pages, 1, page_size, kw];
     every head reads the same rows, a value is a row's first dv entries. `q_lens`: the host's copy of the portions'
-    lengths; `nsplit`: pieces the keys are cut into. Returns [T, nh * dv]."""
+    lengths; `nsplit`: pieces the keys are cut into; `window`: 0, or how many of its last rows a token reads; `sinks` [nh]
+    float32: a sink per head in the denominator. Returns [T, nh * dv]."""
     require_cuda(q, pool, cu_seqlens, ctx_lens, block_table, err)
     pages, one, page_size, kw = pool.shape
     T = q.shape[0]
@@ -298,6 +299,6 @@ def attention_latent(q: torch.Tensor, pool: torch.Tensor, cu_seqlens: torch.Tens
         count_launch()
     check(fn("attention_latent", "cellm_attention_latent")(
         ptr(out), ptr(part_o), ptr(part_ml), ptr(q), ptr(pool), ptr(cu_seqlens), ptr(ctx_lens), ptr(block_table),
-        block_table.stride(0), len(q_lens), T, n_tiles, pages, page_size, nh, kw, dv, float(scale), int(nsplit), ptr(err),
-        stream_of(q)), "attention_latent")
+        block_table.stride(0), len(q_lens), T, n_tiles, pages, page_size, nh, kw, dv, float(scale), int(nsplit), int(window), ptr(sinks),
+        ptr(err), stream_of(q)), "attention_latent")
     return out

@@ -165,6 +165,35 @@ def attention_flash_sink(q: torch.Tensor, cache, ctx, nh: int, nkv: int, hd: int
     return out
 
 
+def attention_flash_masked(q: torch.Tensor, cache, ctx, nh: int, nkv: int, hd: int, scale: float, window: int, keep_first: int,
+                           sinks: Optional[torch.Tensor], gate: Optional[torch.Tensor]) -> torch.Tensor:
+    """The tensor-core attention in its general form (bfloat16; keys and values of one width hd of 32, 64 or 128):
+    position i sees key j <= i with i - j < window or j < keep_first (window 0: every earlier key); `sinks` [nh] float32:
+    one more term exp(sink_h) in a head's denominator; `gate` [T, >= nh] float32 (rows may be strided): head h's output
+    times sigmoid(gate[t, h])."""
+    _f32(sinks, gate)
+    k, v, bt = cache.k, cache.v, cache.block_table
+    if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.shape != k.shape or hd not in (32, 64, 128):
+        raise ValueError("attention_flash_masked: bfloat16 and keys and values of one width of 32, 64 or 128")
+    T, G = q.shape[0], nh // nkv
+    wide = ctx.max_q_len * G > 16
+    rows = 64 if wide else 16
+    n_tiles = sum(-(-n * G // rows) for n in ctx.q_lens)
+    longest = ctx.max_total_len
+    span = min(longest, window + keep_first + ctx.max_q_len) if window > 0 else longest
+    nsplit = max(1, min(-(-span // 128), 296 // max(1, n_tiles * nkv), 32))
+    out = torch.empty((T, nh * hd), dtype=q.dtype, device=q.device)
+    part_o = part_ml = None
+    if nsplit > 1:
+        part_o = torch.empty((nsplit, T * nh, hd), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((nsplit, T * nh, 2), dtype=torch.float32, device=q.device)
+    check(fn("attention_flash", "cellm_attention_flash_masked")(
+        ptr(out), ptr(part_o), ptr(part_ml), ptr(q), ptr(k), ptr(v), ptr(ctx.cu_seqlens), ptr(ctx.ctx_lens), ptr(bt), bt.stride(0),
+        ctx.B, T, n_tiles, k.shape[0], cache.page_size, nh, nkv, hd, float(scale), int(window), int(keep_first), int(wide), nsplit,
+        ptr(sinks), ptr(gate), gate.stride(0) if gate is not None else 0, ptr(ctx.err), stream_of(q)), "attention_flash_masked")
+    return out
+
+
 def hgrn2_scan(proj: torch.Tensor, col_q: int, col_f: int, col_v: int, f_bias: torch.Tensor, lower: torch.Tensor, state: torch.Tensor,
                ctx, heads: int, dim: int, vd: int) -> torch.Tensor:
     """The HGRN2 recurrence over every request's tokens of the step; state [slots, heads, dim, vd] float32 is moved on.

@@ -155,16 +155,19 @@ class SinkAttentionMixer(Mixer):
             ops.conv_state_update(conv_state, proj, 0, self.bias, self.taps, ctx)
         gate = proj[:, proj.shape[1] - self.nh:] if self.gated else None
         tc = self.dtype == torch.bfloat16 and self.hd == self.vd and self.hd in (32, 64, 128) and OPTIONS["tensor_cores"]
-        if tc and not self.keep_first:
+        general = bool(self.keep_first) or self.fixed_sink is not None or gate is not None
+        if tc and (general or self.v_freq is None):
             sinks = self.sinks
-            if self.fixed_sink is not None:
+            if self.fixed_sink is not None:     # one sink score for every head: the kernels take it as a vector
                 if getattr(self, "_fixed", None) is None:
                     self._fixed = torch.full((self.nh,), float(self.fixed_sink), dtype=torch.float32, device=q.device)
                 sinks = self._fixed
-            o = ops.attention_flash_sink(q, pages, ctx, self.nh, self.nkv, self.hd, self.scale, self.window, sinks,
+            if general and self.v_freq is not None:
+                raise ConfigError("sink_attention: rotated values beside kept first keys, a fixed sink or a gate per head")
+            o = ops.attention_flash_masked(q, pages, ctx, self.nh, self.nkv, self.hd, self.scale, self.window, self.keep_first, sinks, gate)
+        elif tc:
+            o = ops.attention_flash_sink(q, pages, ctx, self.nh, self.nkv, self.hd, self.scale, self.window, self.sinks,
                                          self.v_freq, self.interleaved)
-            if gate is not None:
-                ops.head_gate_mul(o, gate, self.nh)
         elif self.keep_first or self.fixed_sink is not None or gate is not None:
             if self.v_freq is not None:
                 raise ConfigError("sink_attention: rotated values beside kept first keys, a fixed sink or a gate per head")

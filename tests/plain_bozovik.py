@@ -97,7 +97,8 @@ def softmax_with_sink(scores, mask, sink):
 def grouped_attention(h, w, p, m, positions, sink, temp=None, size=None, keep_first=0, weights_out=None):
     """Attention with fewer key/value heads than query heads, rotation of part of a head, a sink, a gate per head."""
     T = h.shape[0]
-    H, G, d, vd = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    H, d = m["heads"], m["dim"]
+    G, vd = m.get("kv_heads", H), m.get("vdim", d)
     q = lin(h, w[p + "q"]).view(T, H, d)
     k = lin(h, w[p + "k"]).view(T, G, d)
     v = lin(h, w[p + "v"]).view(T, G, vd)
@@ -192,7 +193,7 @@ def token_side(x, tokens, w, p, layer, dim, eps):
 
 
 def run_layer(x, i, cfg, w, tokens, positions):
-    L, eps, mult, p = cfg["layers"][i], cfg["norm"]["eps"], cfg["residual_mult"], f"l{i}."
+    L, eps, mult, p = cfg["layers"][i], cfg["norm"]["eps"], cfg.get("residual_mult", 1.0), f"l{i}."
     h = layer_norm(x, w[p + "norm1"], w[p + "norm1.b"], eps)
     kind = L["type"]
     if kind == "parallel":
