@@ -64,6 +64,13 @@ __device__ __forceinline__ float cellm_activate(float z, int act) {
     }
 }
 
+// xIELU with its two factors already formed (ap = softplus(p), aq = 1/2 + softplus(q)): z > 0: ap z^2 + z / 2; otherwise
+// aq (exp(z) - 1 - z) + z / 2.
+__device__ __forceinline__ float cellm_softplus(float v) { return v > 20.f ? v : log1pf(expf(v)); }
+__device__ __forceinline__ float cellm_xielu(float z, float ap, float aq) {
+    return z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(aq, expm1f(z) - z, 0.5f * z);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

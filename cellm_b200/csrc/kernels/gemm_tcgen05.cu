@@ -671,12 +671,14 @@ template <> __device__ __forceinline__ void store_half_row<__nv_bfloat16>(__nv_b
 // Grouped form (tile_group given): W holds `groups` matrices of N rows one below the other, and every tile of 128
 // rows of A belongs to one of them, tile_group[row tile] (-1: the tile is empty and skipped by every role alike).
 // This is the product of tokens sorted by the expert they go to, each expert's run padded to whole tiles. act >= 0
-// applies that activation (common.cuh) to the sums before they are stored.
+// applies that activation (common.cuh) to the sums before they are stored; act 6 is xIELU with its two learned numbers
+// read from act_numbers (32-bit, on the device).
 template <int BN, int STAGES, int EPI, typename TO>
 __global__ void __launch_bounds__(192)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                                TO* __restrict__ C, int M, int N, int K, long long ldc, int w_is_static,
-                               int* __restrict__ err, int bn, const int* __restrict__ tile_group, int act) {
+                               int* __restrict__ err, int bn, const int* __restrict__ tile_group, int act,
+                               const float* __restrict__ act_numbers) {
     // bn: the width of a tile in columns, a multiple of 16 (of 128 with the SwiGLU epilogue) and at most BN, which
     // sizes the stages and the accumulators. Widths between the powers of two let the number of tiles come close
     // to a multiple of the SMs, so that the last wave is not half empty.
@@ -799,7 +801,11 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                     if (cols == 32) tmem_ld32(lane_addr + (uint32_t)(c * 32), r);
                     else tmem_ld16(lane_addr + (uint32_t)(c * 32), r);
                     if (c == chunks - 1) { tc_fence_before(); mbar_arrive(&sm.acc_empty2[buf]); }
-                    if (act >= 0) {
+                    if (act == 6) {
+                        const float ap = cellm_softplus(act_numbers[0]), aq = 0.5f + cellm_softplus(act_numbers[1]);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(cellm_xielu(__uint_as_float(r[i]), ap, aq));
+                    } else if (act >= 0) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(cellm_activate(__uint_as_float(r[i]), act));
                     }
@@ -875,7 +881,8 @@ int launch(const CUtensorMap& m_rows, const CUtensorMap& m_cols, TO* C, float* w
 
 template <int BN, int STAGES, int EPI, typename TO>
 int launch_persistent(const CUtensorMap& m_a, const CUtensorMap& m_w, TO* C, int M, int N, int K, long long ldc,
-                      int w_is_static, int* err, cudaStream_t stream, int bn, const int* tile_group = nullptr, int act = -1) {
+                      int w_is_static, int* err, cudaStream_t stream, int bn, const int* tile_group = nullptr, int act = -1,
+                      const float* act_numbers = nullptr) {
     const size_t smem = sizeof(GemmSmem<BN, STAGES>) + 1024;
     static int sms = 0;
     if (sms == 0) {
@@ -889,7 +896,7 @@ int launch_persistent(const CUtensorMap& m_a, const CUtensorMap& m_w, TO* C, int
     const int tiles = ((N + bn - 1) / bn) * ((M + BM - 1) / BM);
     dim3 grid((unsigned)(tiles < sms ? tiles : sms));
     cudaError_t e = cellm_launch(gemm_tcgen05_persistent_kernel<BN, STAGES, EPI, TO>, grid, dim3(192), smem, stream, m_a,
-                                 m_w, C, M, N, K, ldc, w_is_static, err, bn, tile_group, act);
+                                 m_w, C, M, N, K, ldc, w_is_static, err, bn, tile_group, act, act_numbers);
     return e == cudaSuccess ? CELLM_OK : (int)e;
 }
 
@@ -1042,6 +1049,27 @@ CELLM_API int cellm_gemm_grouped_tcgen05(void* C, const void* A, const void* W, 
     }
     if (out_dtype == CELLM_F32) return launch_persistent<256, 4, 0, float>(map_a, map_w, (float*)C, M, N, K, ldc, 0, err, stream, bn, tile_group, act);
     return launch_persistent<256, 4, 0, __nv_bfloat16>(map_a, map_w, (__nv_bfloat16*)C, M, N, K, ldc, 0, err, stream, bn, tile_group, act);
+}
+
+// An ordinary product of any M with xIELU in its epilogue: C [M, N] = xielu(A [M, K] . W [N, K]^T) with the two learned
+// numbers act_numbers = (p, q), 32-bit on the device.
+CELLM_API int cellm_gemm_xielu_tcgen05(void* C, const void* A, const void* W, int M, int N, int K, long long lda, long long ldw,
+                                       long long ldc, int out_dtype, const float* act_numbers, int* err, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return CELLM_OK;
+    if (K <= 0 || (K & 7)) return CELLM_ERR_SIZE;
+    if (!act_numbers) return CELLM_ERR_ARG;
+    if (((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ((lda * 2) & 15) || ((ldw * 2) & 15)) return CELLM_ERR_ALIGN;
+    if (out_dtype != CELLM_F32 && out_dtype != CELLM_BF16) return CELLM_ERR_DTYPE;
+    const int bn = N > 128 ? 256 : 128;
+    CUtensorMap map_a, map_w;
+    if (!tensor_map(&map_a, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, (uint32_t)BM)) return CELLM_ERR_ARG;
+    if (!tensor_map(&map_w, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw * 2, (uint32_t)bn)) return CELLM_ERR_ARG;
+    if (bn == 128) {
+        if (out_dtype == CELLM_F32) return launch_persistent<128, 6, 0, float>(map_a, map_w, (float*)C, M, N, K, ldc, 0, err, stream, bn, nullptr, 6, act_numbers);
+        return launch_persistent<128, 6, 0, __nv_bfloat16>(map_a, map_w, (__nv_bfloat16*)C, M, N, K, ldc, 0, err, stream, bn, nullptr, 6, act_numbers);
+    }
+    if (out_dtype == CELLM_F32) return launch_persistent<256, 4, 0, float>(map_a, map_w, (float*)C, M, N, K, ldc, 0, err, stream, bn, nullptr, 6, act_numbers);
+    return launch_persistent<256, 4, 0, __nv_bfloat16>(map_a, map_w, (__nv_bfloat16*)C, M, N, K, ldc, 0, err, stream, bn, nullptr, 6, act_numbers);
 }
 
 // The product described above gemm_impl.

@@ -49,20 +49,30 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,
 ACTIVATION_CODES = {"gelu": 0, "gelu_tanh": 1, "silu": 2, "relu": 3, "relu2": 4}
 
 
-def gemm_act(a: torch.Tensor, w: torch.Tensor, act: str, out_dtype: torch.dtype) -> torch.Tensor:
+def gemm_act(a: torch.Tensor, w: torch.Tensor, act: str, out_dtype: torch.dtype, act_numbers: torch.Tensor | None = None) -> torch.Tensor:
     """act(a [M, K] . w [N, K]^T) with the activation formed on the 32-bit sums. bfloat16 operands of more than 16 rows:
     the persistent tensor-core product with the activation in its epilogue; otherwise the product with 32-bit output
-    and the activation as a kernel of its own."""
+    and the activation as a kernel of its own. act "xielu" reads its two learned numbers from `act_numbers` (float32,
+    on the device)."""
     M, K = a.shape
+    if act == "xielu" and (act_numbers is None or act_numbers.dtype != torch.float32 or act_numbers.numel() != 2):
+        raise ValueError("gemm_act: xielu wants its two numbers as a float32 tensor")
     if (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and M > 16 and K % 8 == 0 and a.stride(1) == 1 and w.stride(1) == 1
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
             and out_dtype in (torch.bfloat16, torch.float32)):
         from ._state import error_word
         N = w.shape[0]
         c = torch.empty((M, N), dtype=out_dtype, device=a.device)
+        if act == "xielu":
+            check(fn("gemm_tcgen05", "cellm_gemm_xielu_tcgen05")(ptr(c), ptr(a), ptr(w), M, N, K, a.stride(0), w.stride(0), N, tag(out_dtype),
+                                                                ptr(act_numbers), ptr(error_word(a.device)), stream_of(a)), "gemm_xielu_tcgen05")
+            return c
         check(fn("gemm_tcgen05", "cellm_gemm_grouped_tcgen05")(ptr(c), ptr(a), ptr(w), M, N, K, 1, a.stride(0), w.stride(0), N, tag(out_dtype),
                                                               None, ACTIVATION_CODES[act], ptr(error_word(a.device)), stream_of(a)),
               "gemm_grouped_tcgen05")
         return c
+    if act == "xielu":
+        from .stream import xielu
+        return xielu(gemm(a, w, torch.float32), act_numbers, out_dtype)
     from .recurrent import activation
     return activation(gemm(a, w, torch.float32), act, out_dtype)

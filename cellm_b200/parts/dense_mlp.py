@@ -40,13 +40,11 @@ class DenseMLP(FeedForward):
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         from .. import ops
-        if self.act_numbers is not None:
-            return self.down(ops.xielu(self.up(x, out_dtype=torch.float32), self.act_numbers, self.dtype), out_dtype=self.out_dtype)
-        if self.out_dtype is not None:
-            return self.down(ops.activation(self.up(x, out_dtype=torch.float32), self.activation, self.dtype), out_dtype=self.out_dtype)
         if self.up.weight.dtype != x.dtype:          # a matrix kept in 32-bit under bfloat16 activations
-            return self.down(ops.activation(self.up(x, out_dtype=torch.float32), self.activation, self.dtype))
-        return self.down(ops.gemm_act(x, self.up.weight, self.activation, self.dtype))
+            u = self.up(x, out_dtype=torch.float32)
+            h = ops.xielu(u, self.act_numbers, self.dtype) if self.act_numbers is not None else ops.activation(u, self.activation, self.dtype)
+            return self.down(h, out_dtype=self.out_dtype)
+        return self.down(ops.gemm_act(x, self.up.weight, self.activation, self.dtype, self.act_numbers), out_dtype=self.out_dtype)
 
 
 register_feed_forward("dense_mlp", DenseMLP)

@@ -286,7 +286,7 @@ def test_sharp_attention_at_the_edges_and_far_back(tmp_path, dtype):
     a forgotten sink changes the logits outright. The test first asserts, on the plain model, that such rows exist."""
     from cellm_b200.weights import InitSpec
     window, keep = 37, 6
-    scale = 1.2 if dtype == "float32" else 0.5
+    scale = 0.6 if dtype == "float32" else 0.2
     folder = write_model(tmp_path / "sharp", sharp_config(scale, window, keep), 9,
                          init=InitSpec(linear_std=0.25, embedding_std=0.1, bias_std=0.05, norm_jitter=0.1))
     cfg, w = load_plain(folder)
@@ -301,7 +301,7 @@ def test_sharp_attention_at_the_edges_and_far_back(tmp_path, dtype):
     plain.windowed_sink_attention(h0, w, "l0.mix.left.", cfg["layers"][0]["mixer"]["left"], pos, seen)
     W = seen[0]                                                 # [heads, T, T]
     top, where = W[:, 100:].max(-1)
-    assert float(top.median()) > (0.25 if dtype == "float32" else 0.1)
+    assert float(top.median()) > (0.5 if dtype == "float32" else 0.25)
     dist = torch.arange(100, 500)[None] - where
     assert int((dist == window - 1).sum()) >= 3                  # the heaviest key is the window's last
     assert int((where < keep).sum()) >= 3                        # or one of the kept first keys, hundreds of tokens back
@@ -317,9 +317,9 @@ def test_sharp_attention_at_the_edges_and_far_back(tmp_path, dtype):
         for page in (8, 32):
             got = run_trace(folder, dtype, FAMILIES[fam](reqs), page)
             for rid, t in reqs.items():
-                # so peaked a softmax passes a score's last bits on: the plain model itself, run in 32-bit, is 1.6e-4 of the
+                # so peaked a softmax passes a score's last bits on: the plain model itself, run in 32-bit, is 4e-5 of the
                 # logits' size away from its 64-bit run; a lost or surplus key moves a row by a tenth of that size and more
-                against_plain(traces.as_matrix(got[rid], len(t)), ref[rid], dtype, f"sharp {dtype} {fam} page {page} {rid}", k32=2e-4)
+                against_plain(traces.as_matrix(got[rid], len(t)), ref[rid], dtype, f"sharp {dtype} {fam} page {page} {rid}", k32=1e-4)
 
 
 # ------------------------------------------------------------------------------------------ generation
@@ -516,6 +516,21 @@ def test_stream_kernels(T, H):
     o = ops.head_norm_gate(a.to(DEV), w.to(DEV), gw.to(DEV), heads, vd, 1e-5, torch.float32).cpu().double()
     want = (plain.rms(a.double().reshape(T, heads, vd), 1e-5).reshape(T, H) * w.double()) * torch.sigmoid(gw.double())
     torch.testing.assert_close(o, want, rtol=2e-5, atol=2e-5)
+
+
+@pytest.mark.parametrize("M,K,N", [(300, 64, 200), (17, 128, 96), (8, 64, 80), (2048, 256, 1000), (40, 64, 33), (129, 40, 129)])
+def test_product_with_xielu_in_its_epilogue(M, K, N):
+    """The feed-forward's first product with xIELU formed on its 32-bit sums (the tensor-core product's epilogue for prompt
+    portions, a kernel of its own for few rows), against 64-bit torch, in both output types."""
+    from cellm_b200 import ops
+    g = torch.Generator().manual_seed(M + K + N)
+    a = (torch.randn(M, K, generator=g) * 0.7).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.3).to(torch.bfloat16)
+    pq = torch.tensor([0.4, -0.7])
+    want = plain.xielu(a.double() @ w.double().T, pq[0].double(), pq[1].double())
+    for out_dtype, tol in ((torch.float32, 2e-5), (torch.bfloat16, 8e-3)):
+        got = ops.gemm_act(a.to(DEV), w.to(DEV), "xielu", out_dtype, pq.to(DEV)).cpu().double()
+        torch.testing.assert_close(got, want, rtol=tol, atol=tol * float(want.abs().max()))
 
 
 class _Pages:
