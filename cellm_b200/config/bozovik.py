@@ -104,7 +104,7 @@ class LatentAttention:
         rot_dim = _get(d, "rot_dim", int, 0)
         c = cls(_get(d, "heads", int), _get(d, "dim", int), rot_dim, _get(d, "vdim", int), _get(d, "kv_rank", int),
                 _get(d, "scale", float), _get(mask, "size", int, 0), _rot(d, where, rot_dim))
-        if min(c.heads, c.vdim, c.kv_rank) < 1 or c.dim < 0 or c.rot_dim < 0 or c.dim + c.rot_dim < 1 or c.window < 0:
+        if min(c.heads, c.dim, c.vdim, c.kv_rank) < 1 or c.rot_dim < 0 or c.window < 0:
             raise ConfigError(f"config.json: {where}: sizes must be positive")
         return c
 

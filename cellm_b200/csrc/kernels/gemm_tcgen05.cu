@@ -803,8 +803,13 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
                     if (c == chunks - 1) { tc_fence_before(); mbar_arrive(&sm.acc_empty2[buf]); }
                     if (act == 6) {
                         const float ap = cellm_softplus(act_numbers[0]), aq = 0.5f + cellm_softplus(act_numbers[1]);
+                        if constexpr (sizeof(TO) == 2) {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(cellm_xielu(__uint_as_float(r[i]), ap, aq));
+                            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(cellm_xielu_rounded(__uint_as_float(r[i]), ap, aq));
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(cellm_xielu(__uint_as_float(r[i]), ap, aq));
+                        }
                     } else if (act >= 0) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(cellm_activate(__uint_as_float(r[i]), act));
