@@ -39,6 +39,7 @@ class RMSNorm(Norm):
         if self.offset:
             self.weight = (self.weight.to(torch.float32) + self.offset).contiguous()
         self.dtype = dtype
+        self._w32 = self.weight if self.weight.dtype == torch.float32 else None
 
     def emit(self, emitter) -> None:
         from ..ops._lib import tag
@@ -56,7 +57,9 @@ class RMSNorm(Norm):
         """x += mult * addend (in place, 32-bit; None: nothing is added), then the norm of the sum."""
         if self.groups != 1:
             raise ConfigError("rms_norm: an addend times a constant is not taken by a norm in groups")
-        if getattr(self, "_w32", None) is None:
+        if self._w32 is None:       # made at the first use, which must not be a step that is being captured in a graph
+            if torch.cuda.is_available() and torch.cuda.is_current_stream_capturing():
+                raise ConfigError("rms_norm: the 32-bit copy of the weight is made outside a graph's capture")
             self._w32 = self.weight.to(torch.float32).contiguous()
         return ops.add_scaled_norm(x, addend, mult, None, 0.0, "rms", self._w32, None, self.eps, self.dtype)
 

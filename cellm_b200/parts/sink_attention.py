@@ -126,6 +126,11 @@ class SinkAttentionMixer(Mixer):
         if self.eps is not None:
             self.q_norm_w, self.k_norm_w = f32("q_norm"), f32("k_norm")
         self.sinks = f32("sinks") if params.get("sinks", True) else None
+        # one sink score for every head: the tensor-core kernel takes it as a vector (made here, not in a step that may be
+        # captured in a graph)
+        self._fixed = None
+        if self.fixed_sink is not None:
+            self._fixed = torch.full((self.nh,), float(self.fixed_sink), dtype=torch.float32, device=weights["q_proj"].device)
         dev = weights["q_proj"].device
         pos: PartSpec | None = params.get("position")
         self.position = part_class("position", pos.kind)(pos.params, dev) if pos is not None else None
@@ -157,11 +162,7 @@ class SinkAttentionMixer(Mixer):
         tc = self.dtype == torch.bfloat16 and self.hd == self.vd and self.hd in (32, 64, 128) and OPTIONS["tensor_cores"]
         general = bool(self.keep_first) or self.fixed_sink is not None or gate is not None
         if tc and (general or self.v_freq is None):
-            sinks = self.sinks
-            if self.fixed_sink is not None:     # one sink score for every head: the kernels take it as a vector
-                if getattr(self, "_fixed", None) is None:
-                    self._fixed = torch.full((self.nh,), float(self.fixed_sink), dtype=torch.float32, device=q.device)
-                sinks = self._fixed
+            sinks = self.sinks if self.fixed_sink is None else self._fixed
             if general and self.v_freq is not None:
                 raise ConfigError("sink_attention: rotated values beside kept first keys, a fixed sink or a gate per head")
             o = ops.attention_flash_masked(q, pages, ctx, self.nh, self.nkv, self.hd, self.scale, self.window, self.keep_first, sinks, gate)

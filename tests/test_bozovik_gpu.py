@@ -594,10 +594,11 @@ def test_masked_attention_sees_exactly_the_window_and_the_kept_keys(window, keep
         assert abs(float(out[i, 0, 1]) - len(seen) * math.exp(0.5) / (len(seen) * math.exp(0.5) + 1.0)) < 1e-5
 
 
-@pytest.mark.parametrize("hd,window,keep", [(64, 50, 0), (32, 0, 0), (128, 7, 0), (64, 40, 9), (32, 20, 70), (64, 0, 0)])
+@pytest.mark.parametrize("hd,window,keep", [(64, 50, 0), (32, 0, 0), (128, 7, 0), (64, 40, 9), (32, 20, 70), (64, 0, 0), (64, 200, 30), (128, 150, 70)])
 def test_tensor_core_attention_against_the_plain_kernel(tmp_path, hd, window, keep):
     """The bfloat16 mixer (paged mma.sync attention with sink, gate and kept first keys) against the plain kernel on the
-    same cache, for a prompt, portions and single tokens."""
+    same cache, for a prompt, portions and single tokens (windows of 150 and more: a single token's keys are cut into
+    pieces, whose list of blocks starts with the kept keys' blocks)."""
     from cellm_b200.parts import sink_attention as SA
     config = model_config(64, 64, [par(grouped(4, 2, hd, hd, window=window, keep=keep, rot=(10000.0, hd // 2)), 1, 4, rank=2),
                                    attn(4, 1, hd, hd, rot=(10000.0, hd))])
