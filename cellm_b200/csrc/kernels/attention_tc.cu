@@ -222,7 +222,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                     const int* __restrict__ cu_seqlens, const int* __restrict__ ctx_lens,
                     const int* __restrict__ block_table, int bt_stride, int B, int num_pages, int page_size, int nh,
-                    int nkv, float scale_log2e, int window, int* __restrict__ err) {
+                    int nkv, float scale_log2e, int window, const float* __restrict__ sinks, const float* __restrict__ gate,
+                    long long gate_ld, int* __restrict__ err) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     TcSmem& sm = *reinterpret_cast<TcSmem*>(smem_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -482,8 +483,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         if (!ok && lane == 0) { *abort_flag = 1; atomicOr(err, CELLM_DEV_WAIT_TIMEOUT); }
         if (ok) {
             tc_fence_after();
-            const float inv = l > 0.f ? 1.0f / l : 0.f;
-            __nv_bfloat16* dst = out + (size_t)(t_base + tok) * nh * HD + (size_t)(kvh * G + r % G) * HD;
+            // a sink: one more term exp(sink_h) in the row's denominator, against the maximum the row's sums were formed
+            // with; an output gate: the row times the sigmoid of one number per (token, head)
+            const int head = kvh * G + r % G;
+            if (sinks && row_ok) l += exp2f(sinks[head] * 1.4426950408889634f - (m == -INFINITY ? 0.f : m));
+            float inv = l > 0.f ? 1.0f / l : 0.f;
+            if (gate && row_ok) inv *= 1.f / (1.f + __expf(-gate[(size_t)(t_base + tok) * gate_ld + head]));
+            __nv_bfloat16* dst = out + (size_t)(t_base + tok) * nh * HD + (size_t)head * HD;
 #pragma unroll 1
             for (int c = 0; c < HD / 32; ++c) {
                 uint32_t o[32];
@@ -545,10 +551,11 @@ CELLM_API int cellm_attention_tc_supports(int hd, int nh, int nkv, int page_size
 
 // out, q: [T, nh*64] bf16; pools: one layer's [pages][nkv][page_size][64] bf16. n_tiles = sum over the
 // requests of ceil(q_len / (256 / (nh/nkv))): a CTA takes two tiles of 128 rows that share their keys.
-CELLM_API int cellm_attention_tc(void* out, const void* q, const void* k_pool, const void* v_pool,
-                                 const int* cu_seqlens, const int* ctx_lens, const int* block_table, int bt_stride,
-                                 int B, int T, int n_tiles, int num_pages, int page_size, int nh, int nkv, int hd,
-                                 float scale, int window, int* err, cudaStream_t stream) {
+static int attention_tc_impl(void* out, const void* q, const void* k_pool, const void* v_pool,
+                             const int* cu_seqlens, const int* ctx_lens, const int* block_table, int bt_stride,
+                             int B, int T, int n_tiles, int num_pages, int page_size, int nh, int nkv, int hd,
+                             float scale, int window, const float* sinks, const float* gate, long long gate_ld, int* err,
+                             cudaStream_t stream) {
     if (T <= 0 || n_tiles <= 0) return CELLM_OK;
     if (!cellm_attention_tc_supports(hd, nh, nkv, page_size) || scale <= 0.f) return CELLM_ERR_SIZE;
     if (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out) & 15) return CELLM_ERR_ALIGN;
@@ -575,6 +582,26 @@ CELLM_API int cellm_attention_tc(void* out, const void* q, const void* k_pool, c
     }
     dim3 grid((unsigned)n_tiles, (unsigned)nkv);
     CELLM_RUN(attention_tc_kernel, grid, THREADS, smem, stream, mq, mk, mv, (__nv_bfloat16*)out, cu_seqlens,
-              ctx_lens, block_table, bt_stride, B, num_pages, page_size, nh, nkv, scale * 1.4426950408889634f, window, err);
+              ctx_lens, block_table, bt_stride, B, num_pages, page_size, nh, nkv, scale * 1.4426950408889634f, window, sinks,
+              gate, gate_ld, err);
     return CELLM_OK;
+}
+
+CELLM_API int cellm_attention_tc(void* out, const void* q, const void* k_pool, const void* v_pool,
+                                 const int* cu_seqlens, const int* ctx_lens, const int* block_table, int bt_stride,
+                                 int B, int T, int n_tiles, int num_pages, int page_size, int nh, int nkv, int hd,
+                                 float scale, int window, int* err, cudaStream_t stream) {
+    return attention_tc_impl(out, q, k_pool, v_pool, cu_seqlens, ctx_lens, block_table, bt_stride, B, T, n_tiles, num_pages,
+                             page_size, nh, nkv, hd, scale, window, nullptr, nullptr, 0, err, stream);
+}
+
+// The same with a sink per head in every row's denominator (`sinks` [nh], 32-bit; null: none) and an output gate (`gate`
+// [T, gate_ld] 32-bit pre-activations, one per head: the head's output times its sigmoid; null: none).
+CELLM_API int cellm_attention_tc_gated(void* out, const void* q, const void* k_pool, const void* v_pool,
+                                       const int* cu_seqlens, const int* ctx_lens, const int* block_table, int bt_stride,
+                                       int B, int T, int n_tiles, int num_pages, int page_size, int nh, int nkv, int hd,
+                                       float scale, int window, const float* sinks, const float* gate, long long gate_ld,
+                                       int* err, cudaStream_t stream) {
+    return attention_tc_impl(out, q, k_pool, v_pool, cu_seqlens, ctx_lens, block_table, bt_stride, B, T, n_tiles, num_pages,
+                             page_size, nh, nkv, hd, scale, window, sinks, gate, gate_ld, err, stream);
 }

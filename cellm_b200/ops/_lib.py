@@ -78,6 +78,7 @@ _SIGNATURES = {
     "attention_tc": {
         "cellm_attention_tc": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P],
         "cellm_attention_tc_supports": [I, I, I, I],
+        "cellm_attention_tc_gated": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P, L, P, P],
     },
     "attention_flash": {
         "cellm_attention_flash": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, I, P, P],

@@ -89,12 +89,26 @@ def attention_tc_supports(hd: int, nh: int, nkv: int, page_size: int) -> bool:
     return g <= 128 and 128 % g == 0 and page_size in (8, 16, 32, 64, 128)
 
 
+def attention_tc_fills(q_lens: list[int], nh: int, nkv: int, sms: int, min_ctas=None, min_fill: float = 0.5) -> bool:
+    """Whether a step's prompt portions fill the tcgen05 kernel's pairs of 128-row tiles and enough CTAs (the native
+    executor's rule: at least an eighth of the SMs, and half of the tiles' rows in use); below that the mma.sync kernel
+    with its split over the keys fills the GPU better."""
+    per_tile = 256 // (nh // nkv)
+    tiles = sum((n + per_tile - 1) // per_tile for n in q_lens)
+    floor = sms // 8 if min_ctas is None else int(min_ctas)
+    return tiles * nkv >= floor and sum(q_lens) >= min_fill * tiles * per_tile
+
+
 def attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, cu_seqlens: torch.Tensor,
                  ctx_lens: torch.Tensor, block_table: torch.Tensor, q_lens: list[int], nh: int, scale: float,
-                 window: int, err: torch.Tensor) -> torch.Tensor:
+                 window: int, err: torch.Tensor, sinks: torch.Tensor | None = None, gate: torch.Tensor | None = None) -> torch.Tensor:
     """Attention for prompt portions on the tcgen05 tensor cores (scores and outputs in
-    tensor memory): bfloat16, heads of 64; arguments as attention_flash."""
-    require_cuda(q, k_pool, v_pool, cu_seqlens, ctx_lens, block_table, err)
+    tensor memory): bfloat16, heads of 64; arguments as attention_flash. `sinks` [nh] float32: one more term exp(sink_h)
+    in a head's denominator; `gate` [T, >= nh] float32 (rows may be strided): head h's output times sigmoid(gate[t, h])."""
+    require_cuda(q, k_pool, v_pool, cu_seqlens, ctx_lens, block_table, err, sinks)
+    for t in (sinks, gate):
+        if t is not None and t.dtype != torch.float32:
+            raise ValueError("attention_tc: sinks and gate are float32")
     pages, nkv, page_size, hd = k_pool.shape
     if q.dtype != torch.bfloat16 or k_pool.dtype != torch.bfloat16 or q.shape[1] != nh * hd \
             or not attention_tc_supports(hd, nh, nkv, page_size) or scale <= 0:
@@ -102,6 +116,12 @@ def attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, cu
     tok_per_cta = 256 // (nh // nkv)             # a CTA takes two tiles of 128 (token, head) rows
     n_tiles = sum((n + tok_per_cta - 1) // tok_per_cta for n in q_lens)
     out = torch.empty_like(q)
+    if sinks is not None or gate is not None:
+        check(fn("attention_tc", "cellm_attention_tc_gated")(
+            ptr(out), ptr(q), ptr(k_pool), ptr(v_pool), ptr(cu_seqlens), ptr(ctx_lens), ptr(block_table),
+            block_table.stride(0), len(q_lens), q.shape[0], n_tiles, pages, page_size, nh, nkv, hd, float(scale),
+            int(window), ptr(sinks), ptr(gate), gate.stride(0) if gate is not None else 0, ptr(err), stream_of(q)), "attention_tc_gated")
+        return out
     check(fn("attention_tc", "cellm_attention_tc")(
         ptr(out), ptr(q), ptr(k_pool), ptr(v_pool), ptr(cu_seqlens), ptr(ctx_lens), ptr(block_table),
         block_table.stride(0), len(q_lens), q.shape[0], n_tiles, pages, page_size, nh, nkv, hd, float(scale),

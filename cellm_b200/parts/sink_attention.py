@@ -35,8 +35,9 @@ from .registry import part_class, register_mixer
 from .rope import split_inv_freq
 
 
-# Tests turn the tensor-core attention off to compare it with the plain kernel on the same cache.
-OPTIONS = {"tensor_cores": True}
+# Tests turn the tensor-core attention off to compare it with the plain kernel on the same cache, and the tcgen05 kernel
+# off to compare it with the mma.sync one.
+OPTIONS = {"tensor_cores": True, "tcgen05": True}
 
 
 def bindings_of(cache: CacheBinding, n: int) -> tuple:
@@ -147,6 +148,14 @@ class SinkAttentionMixer(Mixer):
             self.v_freq = split_inv_freq(float(params["value_theta"]), self.vd).to(dev)
         self.n_needs = 2 if self.taps > 1 else 1
 
+    def _tcgen05(self, ctx: StepContext, pages: CacheBinding) -> bool:
+        from ..ops._state import sm_count
+        from ..ops.attention import attention_tc_fills, attention_tc_supports
+        from ..runtime.program import OPTIONS as RUN
+        if not OPTIONS["tcgen05"] or self.scale <= 0 or not attention_tc_supports(self.hd, self.nh, self.nkv, pages.page_size):
+            return False
+        return attention_tc_fills(ctx.q_lens, self.nh, self.nkv, sm_count(ctx.device), RUN["attention_tc_min_ctas"], RUN["attention_tc_min_fill"])
+
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
         from .. import ops
         b = bindings_of(cache, self.n_needs)
@@ -165,7 +174,13 @@ class SinkAttentionMixer(Mixer):
             sinks = self.sinks if self.fixed_sink is None else self._fixed
             if general and self.v_freq is not None:
                 raise ConfigError("sink_attention: rotated values beside kept first keys, a fixed sink or a gate per head")
-            o = ops.attention_flash_masked(q, pages, ctx, self.nh, self.nkv, self.hd, self.scale, self.window, self.keep_first, sinks, gate)
+            if not self.keep_first and self._tcgen05(ctx, pages):
+                # prompt portions that fill its tiles: scores and outputs in tensor memory (heads of 64)
+                from ..ops.attention import attention_tc
+                o = attention_tc(q, pages.k, pages.v, ctx.cu_seqlens, ctx.ctx_lens, pages.block_table, ctx.q_lens, self.nh, self.scale,
+                                 self.window, ctx.err, sinks, gate)
+            else:
+                o = ops.attention_flash_masked(q, pages, ctx, self.nh, self.nkv, self.hd, self.scale, self.window, self.keep_first, sinks, gate)
         elif tc:
             o = ops.attention_flash_sink(q, pages, ctx, self.nh, self.nkv, self.hd, self.scale, self.window, self.sinks,
                                          self.v_freq, self.interleaved)

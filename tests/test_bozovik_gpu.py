@@ -618,6 +618,49 @@ def test_tensor_core_attention_against_the_plain_kernel(tmp_path, hd, window, ke
                         f"tensor cores vs plain, {fam} {rid}", k=K_SELF["bfloat16"])
 
 
+def test_tcgen05_attention_with_sinks_and_gate_against_the_mma_kernel(tmp_path):
+    """Prompt portions that fill its tiles run the attention of heads of 64 on tcgen05 (scores and outputs in tensor
+    memory), with the sink in a row's denominator and the gate in its normalisation: against the mma.sync kernel on the same
+    requests, for a windowed attention with learned sinks and for one over every key with a temperature and the fixed sink."""
+    import importlib
+    from cellm_b200.parts import sink_attention as SA
+    from cellm_b200.runtime import program
+    A = importlib.import_module("cellm_b200.ops.attention")      # (the package exports a function of this name)
+    config = model_config(80, 128, [par(grouped(8, 2, 64, 64, window=70, rot=(10000.0, 32)), 1, 8, rank=2, ff=64),
+                                   attn(4, 1, 64, 64, rot=(5000.0, 64), ff=64)], mult=0.7, side=8)
+    folder = write_model(tmp_path / "t", config, 8)
+    cfg, w = load_plain(folder)
+    toks = np.random.default_rng(2).integers(0, 80, 700).tolist()
+    reqs = {"x": toks, "y": toks[100:333]}
+    ref = {rid: Ref(t, cfg, w) for rid, t in reqs.items()}
+    calls = []
+    original = A.attention_tc
+
+    def counting(*a, **k):
+        calls.append(1)
+        return original(*a, **k)
+    A.attention_tc = counting
+    old = program.OPTIONS["attention_tc_min_ctas"]
+    program.OPTIONS["attention_tc_min_ctas"] = 1
+    outs = {}
+    try:
+        for on in (True, False):
+            SA.OPTIONS["tcgen05"] = on
+            n = len(calls)
+            outs[on] = {fam: run_trace(folder, "bfloat16", make(reqs), 16) for fam, make in
+                        (("whole", traces.whole), ("portions", lambda r: traces.portions(r, (300, 64, 130, 2))))}
+            assert (len(calls) > n) == on
+    finally:
+        SA.OPTIONS["tcgen05"] = True
+        program.OPTIONS["attention_tc_min_ctas"] = old
+        A.attention_tc = original
+    for fam in outs[True]:
+        for rid, t in reqs.items():
+            against_plain(traces.as_matrix(outs[True][fam][rid], len(t)), ref[rid], "bfloat16", f"tcgen05 {fam} {rid}")
+            check_close(traces.as_matrix(outs[True][fam][rid], len(t)), traces.as_matrix(outs[False][fam][rid], len(t)), "bfloat16",
+                        f"tcgen05 vs mma.sync, {fam} {rid}", k=K_SELF["bfloat16"])
+
+
 def test_config_reader_takes_what_the_file_leaves_out(tmp_path):
     """No loop, no side input, no mask, no rotation, no kv_heads: none of them exists then."""
     from cellm_b200.config import config_from_dict
