@@ -458,7 +458,7 @@ CELLM_API int cellm_attention_flash_sink(void* out, float* part_o, float* part_m
 }
 
 // The general form: a learned sink per head (`sinks`; a fixed sink is a vector of one score), the sequence's first
-// `keep_first` keys visible behind the window (position i sees j <= i with i - j < window or j < keep_first), and an output
+// `keep_first` keys visible behind the window (from position i a key j <= i is visible when i - j < window or j < keep_first), and an output
 // gate (`gate` [T, gate_ld] 32-bit pre-activations, one per head; null: none).
 CELLM_API int cellm_attention_flash_masked(void* out, float* part_o, float* part_ml, const void* q, const void* k_pool,
                                            const void* v_pool, const int* cu_seqlens, const int* ctx_lens,

@@ -209,7 +209,7 @@ CELLM_API int cellm_attention_plain_sink(void* out, const void* q, const void* k
                                 hd, hdv, hdv, scale, window, dtype, err, stream, sinks, unrot, interleaved);
 }
 
-// The general form: a window that keeps the sequence's first `keep_first` keys visible (position i sees j <= i with
+// The general form: a window that keeps the sequence's first `keep_first` keys visible (from position i a key j <= i is visible when
 // i - j < window or j < keep_first; window 0: every earlier key), a learned sink per head (`sinks`) or one fixed sink
 // score for all heads (`has_fixed_sink`), an output gate (`gate` [T, gate_ld] 32-bit pre-activations, one per head: the
 // head's output is multiplied by its sigmoid; null: none), and value rows `v_row` wide of which the first hdv entries are

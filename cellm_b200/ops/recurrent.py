@@ -119,7 +119,7 @@ def attention_plain_sink(q: torch.Tensor, cache, ctx, nh: int, nkv: int, hd: int
 def attention_plain_masked(q: torch.Tensor, cache, ctx, nh: int, nkv: int, hd: int, vd: int, scale: float, window: int = 0,
                            keep_first: int = 0, sinks: Optional[torch.Tensor] = None, fixed_sink: Optional[float] = None,
                            gate: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """The plain attention in its general form: position i sees key j <= i with i - j < window or j < keep_first (window 0:
+    """The plain attention in its general form: from position i a key j <= i is visible when i - j < window or j < keep_first (window 0:
     every earlier key); `sinks` [nh] float32 (a learned sink per head) or `fixed_sink` (one sink score for all heads) is
     one more term in the denominator; `gate` [T, >= nh] float32 (rows may be strided): head h's output times
     sigmoid(gate[t, h]). A cache without a pool of values gives its key rows' first vd entries as values."""
@@ -168,7 +168,7 @@ def attention_flash_sink(q: torch.Tensor, cache, ctx, nh: int, nkv: int, hd: int
 def attention_flash_masked(q: torch.Tensor, cache, ctx, nh: int, nkv: int, hd: int, scale: float, window: int, keep_first: int,
                            sinks: Optional[torch.Tensor], gate: Optional[torch.Tensor]) -> torch.Tensor:
     """The tensor-core attention in its general form (bfloat16; keys and values of one width hd of 32, 64 or 128):
-    position i sees key j <= i with i - j < window or j < keep_first (window 0: every earlier key); `sinks` [nh] float32:
+    from position i a key j <= i is visible when i - j < window or j < keep_first (window 0: every earlier key); `sinks` [nh] float32:
     one more term exp(sink_h) in a head's denominator; `gate` [T, >= nh] float32 (rows may be strided): head h's output
     times sigmoid(gate[t, h])."""
     _f32(sinks, gate)

@@ -9,7 +9,7 @@ Since q_h . (K_h c) = (K_h^T q_h) . c, the attention runs over the cached rows t
 the query of head h becomes [K_h^T q_h | rotated part], the weighted sum of the rows' first kv_rank values is formed,
 and V_h turns it into the head's output. The rotation is a position part of its own (`position`), applied to the last
 rot_dim values of each query head and to the shared key part, in pairs that lie side by side or half a rotation apart.
-Optional: a sliding window (position i sees the rows j with 0 <= i - j < window; rows that no later token can read give
+Optional: a sliding window (from position i the rows j with 0 <= i - j < window are visible; rows that no later token can read give
 their pages back) and a learned sink per head (one more term exp(sink_h) in the softmax's denominator, with no key and
 no value)."""
 from __future__ import annotations

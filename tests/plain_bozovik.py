@@ -77,7 +77,7 @@ def rotate_half(x, positions, base, dims):
 
 
 def visible(T, size=None, keep_first=0):
-    """[T, T] mask: row i sees column j when j <= i and (size is None, or i - j < size, or j < keep_first)."""
+    """[T, T] mask: entry [i, j] is true when j <= i and (size is None, or i - j < size, or j < keep_first)."""
     i = torch.arange(T)[:, None]
     j = torch.arange(T)[None, :]
     m = j <= i
