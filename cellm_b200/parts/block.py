@@ -251,6 +251,7 @@ class ScaledPreNormBlock(Block):
                 raise ConfigError("pre_norm_scaled: more passes than step vectors")
 
     def forward(self, residual: Residual, ctx: StepContext, cache: CacheBinding) -> None:
+        import torch
         from .. import ops
         x = residual.flush()
         if self.passes:
@@ -266,14 +267,9 @@ class ScaledPreNormBlock(Block):
             return
         # x += m * a, and the sum in the activations' type for the gate's product
         xb = ops.add_scaled_norm(x, a.contiguous(), m, None, 0.0, "none", None, None, 0.0, self.dtype)
-        g = self.token_gate(xb, out_dtype=torch_float32())
+        g = self.token_gate(xb, out_dtype=torch.float32)
         e = ops.token_gate_mul(g, self.token_table, self.token_offset, ctx.token_ids, self.token_act, self.dtype, ctx.err)
-        ops.scaled_rms_add(x, self.token_proj(e, out_dtype=torch_float32()), self.token_norm, m, self.token_eps)
-
-
-def torch_float32():
-    import torch
-    return torch.float32
+        ops.scaled_rms_add(x, self.token_proj(e, out_dtype=torch.float32), self.token_norm, m, self.token_eps)
 
 
 register_block("pre_norm_scaled", ScaledPreNormBlock)
